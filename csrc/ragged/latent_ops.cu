@@ -6,6 +6,7 @@
 //
 //   embed_sinusoid        token table lookup + sinusoidal position vector -> fp32 residual
 //   sandwich_norm         x += rms(y) * (wb + ob)   and / or   out = rms(x) * (w + o)      (one pass per token row)
+//   stream_group_norm     x += y0 + y1 + y2         and / or   out = rms-in-groups(x) * w      (blocks whose sublayers share one norm)
 //   latent_norm_append    plain-weight RMS norm of the query latent and of the key/value latent of every token; the
 //                         key/value latent goes straight into its slot of the paged latent cache
 //   latent_attention      softmax(q_abs . c) c over the paged latent cache: all heads of a token share the cached rows
@@ -68,21 +69,21 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ---------------------------------------------------------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_sinusoid_kernel(const long long* __restrict__ ids, const TW* __restrict__ table, const int* __restrict__ tok_pos,
-                                      const double* __restrict__ freq, float* __restrict__ out, int dim) {
+                                      const double* __restrict__ freq, float* __restrict__ out, int dim, float scale) {
   const int t = blockIdx.x;
   const long long id = ids[t];
   const TW* row = table + id * dim;
   float* o = out + static_cast<size_t>(t) * dim;
   if (freq == nullptr) {  // no position vector: the table row alone starts the stream (tok_pos may be null)
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = to_f(row[i]);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = to_f(row[i]) * scale;
     return;
   }
   const double p = static_cast<double>(tok_pos[t]);
   for (int i = threadIdx.x; 2 * i < dim; i += blockDim.x) {
     double s, c;
     sincos(p * freq[i], &s, &c);
-    o[2 * i] = to_f(row[2 * i]) + static_cast<float>(s);
-    if (2 * i + 1 < dim) o[2 * i + 1] = to_f(row[2 * i + 1]) + static_cast<float>(c);
+    o[2 * i] = to_f(row[2 * i]) * scale + static_cast<float>(s);
+    if (2 * i + 1 < dim) o[2 * i + 1] = to_f(row[2 * i + 1]) * scale + static_cast<float>(c);
   }
 }
 
@@ -222,6 +223,97 @@ __global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __rest
       const float4 v = make_float4(xv[i].x * inv * (g.x + o), xv[i].y * inv * (g.y + o), xv[i].z * inv * (g.z + o), xv[i].w * inv * (g.w + o));
       store4(orow + 4 * c, v);
       if (out32) store4(out32 + static_cast<size_t>(r) * dim + 4 * c, v);
+    }
+  }
+}
+
+// Blocks whose sublayers all read ONE norm of the stream and whose outputs are summed into it: output row r works on row src = rows[r] of the
+// fp32 residual and of the branches (src = r without `rows`).  First the finished sublayers' outputs join the stream,
+//   x <- x + y0 + y1 + y2        (y0, y1 in the activation dtype, y2 fp32; each may be null; the sum is fp32; written back only without `rows`),
+// then, when w is given, the row is split into `groups` equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps), and
+// the whole multiplied by w: out in the activation dtype, out32 (optional) the same values before rounding.  The summed row is kept in
+// shared memory (dim floats) between the two steps.
+template <typename TY, typename TO>
+__global__ void stream_group_norm_kernel(float* __restrict__ x, const TY* __restrict__ y0, const TY* __restrict__ y1, const float* __restrict__ y2,
+                                         const float* __restrict__ w, TO* __restrict__ out, float* __restrict__ out32,
+                                         const int* __restrict__ rows, int dim, int groups, float eps) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const size_t so = static_cast<size_t>(rows ? rows[r] : r) * dim, o = static_cast<size_t>(r) * dim;
+  const bool add = y0 != nullptr || y1 != nullptr || y2 != nullptr;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float v = x[so + c];
+    if (y0) v += to_f(y0[so + c]);
+    if (y1) v += to_f(y1[so + c]);
+    if (y2) v += y2[so + c];
+    if (add && rows == nullptr) x[so + c] = v;
+    rowbuf[c] = v;  // read back below by this same thread only
+  }
+  if (w == nullptr) return;
+  const int per = dim / groups;
+  for (int g = 0; g < groups; ++g) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < per; c += blockDim.x) {
+      const float v = rowbuf[g * per + c];
+      s += v * v;
+    }
+    s = block_sum(s, red);
+    const float inv = 1.f / sqrtf(s / static_cast<float>(per) + eps);
+    for (int c = threadIdx.x; c < per; c += blockDim.x) {
+      const float v = rowbuf[g * per + c] * inv * w[g * per + c];
+      out[o + g * per + c] = from_f<TO>(v);
+      if (out32) out32[o + g * per + c] = v;
+    }
+  }
+}
+
+// The same for parts that are multiples of 128 values and dim <= 4 * SN_MAXV * blockDim: 16-byte accesses, the row is read once and kept
+// in registers; the 128 consecutive values a warp holds per step lie in one part, so a part's sum is a warp reduction plus one
+// shared-memory add per warp and step.
+constexpr int GN_MAXG = 32;
+template <typename TY, typename TO>
+__global__ void stream_group_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y0, const TY* __restrict__ y1,
+                                             const float* __restrict__ y2, const float* __restrict__ w, TO* __restrict__ out,
+                                             float* __restrict__ out32, const int* __restrict__ rows, int dim, int groups, float eps) {
+  __shared__ float gsum[GN_MAXG];
+  const int r = blockIdx.x, lane = threadIdx.x & 31;
+  const size_t so = static_cast<size_t>(rows ? rows[r] : r) * dim, o = static_cast<size_t>(r) * dim;
+  const int nv = dim >> 2, per = dim / groups;
+  const bool add = y0 != nullptr || y1 != nullptr || y2 != nullptr;
+  if (threadIdx.x < groups) gsum[threadIdx.x] = 0.f;
+  __syncthreads();
+  float4 xv[SN_MAXV];
+#pragma unroll
+  for (int i = 0; i < SN_MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    float s = 0.f;
+    if (c < nv) {
+      float4 v = load4(x + so + 4 * c);
+      if (y0) { const float4 a = load4(y0 + so + 4 * c); v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
+      if (y1) { const float4 a = load4(y1 + so + 4 * c); v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
+      if (y2) { const float4 a = load4(y2 + so + 4 * c); v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
+      if (add && rows == nullptr) store4(x + so + 4 * c, v);
+      xv[i] = v;
+      s = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (w != nullptr) {
+      s = warp_sum(s);
+      const int c0 = (threadIdx.x - lane) + i * blockDim.x;  // the warp's first 4-vector of this step
+      if (lane == 0 && c0 < nv) atomicAdd(&gsum[(4 * c0) / per], s);
+    }
+  }
+  if (w == nullptr) return;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < SN_MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nv) {
+      const float inv = 1.f / sqrtf(gsum[(4 * c) / per] / static_cast<float>(per) + eps);
+      const float4 g = load4(w + 4 * c);
+      const float4 v = make_float4(xv[i].x * inv * g.x, xv[i].y * inv * g.y, xv[i].z * inv * g.z, xv[i].w * inv * g.w);
+      store4(out + o + 4 * c, v);
+      if (out32) store4(out32 + o + 4 * c, v);
     }
   }
 }
@@ -475,6 +567,20 @@ __global__ void clamped_swish_gate_vec_kernel(const T* __restrict__ gu, T* __res
   }
 }
 
+// The same on column ranges: gate at column gate_col0 and up at column up_col0 of gu [rows, ld], result into out [rows, out_ld] (a view)
+template <typename T>
+__global__ void clamped_swish_gate_cols_kernel(const T* __restrict__ gu, long long ld, int gate_col0, int up_col0, T* __restrict__ out,
+                                               long long out_ld, long long rows, int F, float alpha, float limit, float shift) {
+  const long long n = rows * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / F;
+    const int c = static_cast<int>(i % F);
+    const float g = fminf(to_f(gu[r * ld + gate_col0 + c]), limit);
+    const float u = fminf(fmaxf(to_f(gu[r * ld + up_col0 + c]), -limit), limit);
+    out[r * out_ld + c] = from_f<T>(g * (1.f / (1.f + expf(-alpha * g))) * (u + shift));
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, long long ld, int cols, long long n, float cap) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float* p = x + (i / cols) * ld + (i % cols);
@@ -593,14 +699,18 @@ __global__ void moe_scatter_kernel(const T* __restrict__ x, const int* __restric
 
 template <typename T, bool VEC>
 __global__ void moe_gather_kernel(const T* __restrict__ moe_out, const float* __restrict__ scores, const int* __restrict__ mapped_slots,
-                                  float* __restrict__ out, int dim, int K) {
+                                  float* __restrict__ out, int dim, int K, const int* __restrict__ assignments, int n_real,
+                                  const float* __restrict__ identity_src) {
   const int t = blockIdx.x;
+  // experts n_real and above are identity experts: their output is the token's own row of identity_src (fp32)
   if constexpr (VEC) {
     for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int k = 0; k < K; ++k) {
         const float s = scores ? scores[t * K + k] : 1.f;
-        const float4 v = load4(moe_out + static_cast<size_t>(mapped_slots[t * K + k]) * dim + c);
+        const bool same = assignments != nullptr && assignments[t * K + k] >= n_real;
+        const float4 v = same ? load4(identity_src + static_cast<size_t>(t) * dim + c)
+                              : load4(moe_out + static_cast<size_t>(mapped_slots[t * K + k]) * dim + c);
         acc.x = fmaf(s, v.x, acc.x); acc.y = fmaf(s, v.y, acc.y); acc.z = fmaf(s, v.z, acc.z); acc.w = fmaf(s, v.w, acc.w);
       }
       store4(out + static_cast<size_t>(t) * dim + c, acc);
@@ -608,8 +718,11 @@ __global__ void moe_gather_kernel(const T* __restrict__ moe_out, const float* __
   } else {
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
       float acc = 0.f;
-      for (int k = 0; k < K; ++k)
-        acc = fmaf(scores ? scores[t * K + k] : 1.f, to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]), acc);
+      for (int k = 0; k < K; ++k) {
+        const bool same = assignments != nullptr && assignments[t * K + k] >= n_real;
+        const float v = same ? identity_src[static_cast<size_t>(t) * dim + c] : to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]);
+        acc = fmaf(scores ? scores[t * K + k] : 1.f, v, acc);
+      }
       out[static_cast<size_t>(t) * dim + c] = acc;
     }
   }
@@ -697,14 +810,14 @@ static inline int grid_for(long long n, int block) {
 
 // out[t, :] = table[ids[t], :] + sinusoid(tok_pos[t]): entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i); `freq` holds the
 // ceil(dim / 2) frequencies as doubles on the device, or is null for no position vector (tok_pos is then unused).
-// table_dtype: 0 = bf16, 1 = fp32.  out is fp32.
+// table_dtype: 0 = bf16, 1 = fp32.  out is fp32.  The table row is multiplied by `scale` (in fp32) before the position vector is added.
 DSB_EXPORT int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
-                                     float* out, int n_tokens, int dim, cudaStream_t stream) {
+                                     float* out, int n_tokens, int dim, float scale, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
   if (table_dtype == 0)
-    embed_sinusoid_kernel<bf16><<<n_tokens, 128, 0, stream>>>(ids, (const bf16*)table, tok_pos, freq, out, dim);
+    embed_sinusoid_kernel<bf16><<<n_tokens, 128, 0, stream>>>(ids, (const bf16*)table, tok_pos, freq, out, dim, scale);
   else
-    embed_sinusoid_kernel<float><<<n_tokens, 128, 0, stream>>>(ids, (const float*)table, tok_pos, freq, out, dim);
+    embed_sinusoid_kernel<float><<<n_tokens, 128, 0, stream>>>(ids, (const float*)table, tok_pos, freq, out, dim, scale);
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }
@@ -731,6 +844,45 @@ DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const 
   do {                                                                                                                              \
     if (vec) sandwich_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, y_mult, w, o, (TO*)out, out32, rows, dim, eps, plain_out); \
     else sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, y_mult, w, o, (TO*)out, out32, rows, dim, eps, plain_out);  \
+  } while (0)
+  if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
+  else if (y_dtype == 0) LAUNCH(bf16, float);
+  else if (out_dtype == 0) LAUNCH(float, bf16);
+  else LAUNCH(float, float);
+#undef LAUNCH
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Output row r works on row src = rows[r] (src = r without `rows`) of the fp32 residual x and of the branches: x[src] + y0[src] + y1[src] +
+// y2[src] (each branch optional; y0 and y1 in dtype y_dtype, y2 fp32) -- written back to x only without `rows` -- then, if w: out[r] = that
+// row split into `groups` equal consecutive parts, each over its own root mean square (eps inside the root), times w.  out bf16
+// (out_dtype 0) or fp32 (1); out32 (optional) the same values before rounding.
+DSB_EXPORT int dsb200_stream_group_norm(float* x, const void* y0, const void* y1, int y_dtype, const float* y2, const float* w, void* out,
+                                        int out_dtype, float* out32, const int* rows, int n_rows, int dim, int groups, float eps,
+                                        cudaStream_t stream) {
+  if (n_rows == 0) return DSB_OK;
+  DSB_REQUIRE(groups >= 1 && dim % groups == 0, "stream_group_norm: %d values do not split into %d equal parts", dim, groups);
+  DSB_REQUIRE(w == nullptr || out != nullptr, "stream_group_norm: a norm needs an output");
+  const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y0) | reinterpret_cast<uintptr_t>(y1) | reinterpret_cast<uintptr_t>(y2) |
+                        reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out32);
+  const bool vec = (dim / groups) % 128 == 0 && groups <= GN_MAXG && dim <= 4 * SN_MAXV * 512 && (all & 15) == 0;
+  int block = dim >= 1024 ? 256 : 128;
+  if (vec) {
+    block = 64;
+    while (block * SN_MAXV * 4 < dim) block *= 2;
+  }
+  const size_t smem = vec ? 0 : static_cast<size_t>(dim) * sizeof(float);
+  DSB_REQUIRE(smem <= 200 * 1024, "stream_group_norm: a row of %d values does not fit shared memory", dim);
+#define LAUNCH(TY, TO)                                                                                                                       \
+  do {                                                                                                                                       \
+    if (vec) {                                                                                                                               \
+      stream_group_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y0, (const TY*)y1, y2, w, (TO*)out, out32, rows, dim, groups, eps); \
+    } else {                                                                                                                                 \
+      if (smem > 48 * 1024)                                                                                                                  \
+        DSB_CHECK_CUDA(cudaFuncSetAttribute(stream_group_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
+      stream_group_norm_kernel<TY, TO><<<n_rows, block, smem, stream>>>(x, (const TY*)y0, (const TY*)y1, y2, w, (TO*)out, out32, rows, dim, groups, eps); \
+    }                                                                                                                                        \
   } while (0)
   if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
   else if (y_dtype == 0) LAUNCH(bf16, float);
@@ -862,6 +1014,22 @@ DSB_EXPORT int dsb200_clamped_swish_gate(const void* gu, void* out, long long ro
   return DSB_OK;
 }
 
+// out[r, c] = g' * sigmoid(alpha g') * (clamp(u, -limit, limit) + shift) with g' = min(gu[r, gate_col0 + c], limit), u = gu[r, up_col0 + c], c < F:
+// gate and up are column ranges of one fused projection gu [rows, ld]; out [rows, out_ld] may be a column range of a wider buffer.
+DSB_EXPORT int dsb200_clamped_swish_gate_cols(const void* gu, long long ld, int gate_col0, int up_col0, void* out, long long out_ld, long long rows,
+                                              int F, float alpha, float limit, float shift, int dtype, cudaStream_t stream) {
+  const long long n = rows * F;
+  if (n == 0) return DSB_OK;
+  if (dtype == 0)
+    clamped_swish_gate_cols_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gu, ld, gate_col0, up_col0, (bf16*)out, out_ld, rows, F, alpha,
+                                                                              limit, shift);
+  else
+    clamped_swish_gate_cols_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)gu, ld, gate_col0, up_col0, (float*)out, out_ld, rows, F,
+                                                                               alpha, limit, shift);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
 // x[r, c] = cap * tanh(x[r, c] / cap) over fp32 [rows, cols] with row stride ld
 DSB_EXPORT int dsb200_softcap(float* x, long long ld, long long rows, int cols, float cap, cudaStream_t stream) {
   const long long n = rows * cols;
@@ -911,12 +1079,15 @@ DSB_EXPORT int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, 
   return DSB_OK;
 }
 
-// out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]; scores may be null (plain sum)
+// out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]; scores may be null (plain sum).  With `assignments` (the chosen
+// expert of every (token, k)): experts n_real and above are identity experts whose output is the token's row of identity_src (fp32
+// [n_tokens, dim]) instead of a row of moe_out.
 DSB_EXPORT int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens, int dim,
-                                      int top_k, int dtype, cudaStream_t stream) {
+                                      int top_k, int dtype, const int* assignments, int n_real, const float* identity_src, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
-  const bool vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(moe_out) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-#define LAUNCH(T, V) moe_gather_kernel<T, V><<<n_tokens, 256, 0, stream>>>((const T*)moe_out, scores, mapped_slots, out, dim, top_k)
+  DSB_REQUIRE(assignments == nullptr || identity_src != nullptr, "moe_gather_rows: identity experts need their source rows");
+  const bool vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(moe_out) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(identity_src)) & 15) == 0;
+#define LAUNCH(T, V) moe_gather_kernel<T, V><<<n_tokens, 256, 0, stream>>>((const T*)moe_out, scores, mapped_slots, out, dim, top_k, assignments, n_real, identity_src)
   if (dtype == 0 && vec) LAUNCH(bf16, true);
   else if (dtype == 0) LAUNCH(bf16, false);
   else if (vec) LAUNCH(float, true);

@@ -18,7 +18,9 @@
 //                         o = S^T q / (max(|n . q|, exp(-m)) + 1e-6)
 //   delta_prepare         short convolution + silu of q / k / v projections, unit-length q and k per head
 //   delta_rule_scan       S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, one decay per head and key channel
-//   head_norm_gate        per-head RMS norm of the fp32 read-out, times a weight, times sigmoid(gate), times a constant
+//   tied_gate_scan        S <- diag(f) S + (1 - f) v^T; o = S^T q: the forget gate f of every key channel also sets what is written
+//                         (q = silu, f = lower + (1 - lower) sigmoid, both formed from the fused projection while it is staged)
+//   head_norm_gate        per-head RMS norm of the fp32 read-out, times a weight, times sigmoid(gate) when there is one, times a constant
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -613,6 +615,119 @@ delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ k
   }
 }
 
+// Linear attention whose forget gate also decides what is written (no key projection): per head, with the fused projection proj [T, ld]
+// holding the query pre-activations [H d] at q_col0, the gate pre-activations [H d] at f_col0 and the values [H dv] at v_col0,
+//   q = silu(q_pre),  f = lower + (1 - lower) sigmoid(f_pre + f_bias),  S <- diag(f) S + (1 - f) v^T,  o = S^T q.
+// The activations are formed in fp32 while a chunk is fetched; state layout, chunking and the thread mapping are those of the other scans.
+template <typename T, int RPT, int R>
+__global__ void __launch_bounds__(SCAN_THREADS, RPT <= 16 ? 2 : 1)
+tied_gate_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int f_col0, int v_col0, const float* __restrict__ f_bias,
+                      const float* __restrict__ lower, const int4* __restrict__ seq_desc, float* __restrict__ state_S, float* __restrict__ out,
+                      int H, int d, int dv, int ch) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int nthr = SCAN_THREADS, CB = nthr / R, CBT = SCAN_CPT * CB, DP = R * RPT;
+  const int4 sd = seq_desc[blockIdx.x];
+  const int h = blockIdx.y, tid = threadIdx.x;
+  const int col0 = blockIdx.z * CBT, lc = tid / R, r = tid % R, col = col0 + lc;  // the thread's columns: col and col + CB
+  const bool live = col < dv, live2 = col + CB < dv;
+  const int ncol = min(CBT, dv - col0);
+  const int buf = 2 * ch * DP + ch * CBT;  // q | f | v
+  if (d != DP)
+    for (int x = tid; x < 2 * buf; x += nthr) sm[x] = 0.f;  // padded rows: q = 0 (they never reach the output), f = 0
+  float S[RPT], S2[RPT];
+  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * SCAN_CPT * RPT * nthr;
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) {
+    S[ii] = sd.z > 0 ? gS[ii * nthr + tid] : 0.f;
+    S2[ii] = sd.z > 0 ? gS[(RPT + ii) * nthr + tid] : 0.f;
+  }
+  const int lg_d = (d & (d - 1)) == 0 ? __ffs(d) - 1 : -1, lg_c = (ncol & (ncol - 1)) == 0 ? __ffs(ncol) - 1 : -1;
+  auto split_qk = [&](int x, int& tok, int& c) {
+    if (lg_d >= 0) { tok = x >> lg_d; c = x & (d - 1); } else { tok = x / d; c = x - tok * d; }
+  };
+  auto split_v = [&](int x, int& tok, int& c) {
+    if (lg_c >= 0) { tok = x >> lg_c; c = x & (ncol - 1); } else { tok = x / ncol; c = x - tok * ncol; }
+  };
+  float pq[SCAN_PF], pf[SCAN_PF], pv[SCAN_PF];
+  const float *fb = f_bias + h * d, *lo = lower + h * d;
+  auto fetch = [&](int t0) {
+    const int cn = min(ch, sd.y - t0);
+    const T* row0 = proj + static_cast<size_t>(sd.x + t0) * ld;
+#pragma unroll
+    for (int e = 0; e < SCAN_PF; ++e) {
+      int tok, c;
+      split_qk(tid + e * nthr, tok, c);
+      if (tok < cn) {
+        const T* pr = row0 + static_cast<size_t>(tok) * ld;
+        pq[e] = siluf_(to_f(pr[q_col0 + h * d + c]));
+        const float l = lo[c];
+        pf[e] = l + (1.f - l) * sigmoidf_(to_f(pr[f_col0 + h * d + c]) + fb[c]);
+      }
+      split_v(tid + e * nthr, tok, c);
+      if (tok < cn) pv[e] = to_f(row0[static_cast<size_t>(tok) * ld + v_col0 + h * dv + col0 + c]);
+    }
+  };
+  auto stage = [&](int t0, float* bq) {
+    const int cn = min(ch, sd.y - t0);
+    float* bf = bq + ch * DP;
+    float* bv = bf + ch * DP;
+#pragma unroll
+    for (int e = 0; e < SCAN_PF; ++e) {
+      int tok, c;
+      split_qk(tid + e * nthr, tok, c);
+      if (tok < cn) {
+        const int pos = tok * DP + staged_pos<RPT, R>(c);
+        bq[pos] = pq[e];
+        bf[pos] = pf[e];
+      }
+      split_v(tid + e * nthr, tok, c);
+      if (tok < cn) bv[tok * CBT + c] = pv[e];
+    }
+  };
+  __syncthreads();  // the zeros are in place
+  fetch(0);
+  stage(0, sm);
+  __syncthreads();
+  int cur = 0;
+  for (int t0 = 0; t0 < sd.y; t0 += ch, cur ^= 1) {
+    const int cn = min(ch, sd.y - t0);
+    const bool more = t0 + ch < sd.y;
+    if (more) fetch(t0 + ch);
+    const float* bq = sm + cur * buf + r * 4;
+    const float* bf = bq + ch * DP;
+    const float* bv = sm + cur * buf + 2 * ch * DP;
+    float* orow = out + static_cast<size_t>(sd.x + t0) * H * dv + h * dv + col;
+    for (int x = 0; x < cn; ++x) {
+      const float v1 = live ? bv[x * CBT + lc] : 0.f, v2 = live2 ? bv[x * CBT + CB + lc] : 0.f;
+      float po = 0.f, po2 = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < RPT; i4 += 4) {
+        const float4 f4 = *reinterpret_cast<const float4*>(bf + x * DP + i4 * R), q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4 * R);
+        const float ff[4] = {f4.x, f4.y, f4.z, f4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float w = 1.f - ff[j];
+          S[i4 + j] = fmaf(ff[j], S[i4 + j], w * v1);
+          S2[i4 + j] = fmaf(ff[j], S2[i4 + j], w * v2);
+          po = fmaf(S[i4 + j], qq[j], po);
+          po2 = fmaf(S2[i4 + j], qq[j], po2);
+        }
+      }
+      po = lanes_sum<R>(po);
+      po2 = lanes_sum<R>(po2);
+      if (live && r == 0) orow[static_cast<size_t>(x) * H * dv] = po;
+      if (live2 && r == 0) orow[static_cast<size_t>(x) * H * dv + CB] = po2;
+    }
+    if (more) stage(t0 + ch, sm + (cur ^ 1) * buf);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) {
+    gS[ii * nthr + tid] = S[ii];
+    gS[(RPT + ii) * nthr + tid] = S2[ii];
+  }
+}
+
 // One block per token.  proj row holds the q [G d], k [G d] and v [H dv] projections at q_col0 / k_col0 / v_col0; the kept rows of the
 // sequence are [taps - 1, 2 G d + H dv] (q | k | v channels).  Each goes through its short convolution and silu; q and k are then made unit
 // vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2: a warp takes a head at a time, so the sums need no atomics.  The same
@@ -670,6 +785,7 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, i
 }
 
 // One warp per (token, head): out[t, col0 + h dv + c] = o / sqrt(mean_c(o^2) + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult
+// (gate null: no gate factor)
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_stride, const T* __restrict__ gate,
                                       long long gate_ld, T* __restrict__ out, long long out_ld, int n_tokens, int H, int dv, float eps, float mult) {
@@ -681,9 +797,9 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   for (int c = lane; c < dv; c += 32) s += orow[c] * orow[c];
   s = warp_sum(s);
   const float inv = 1.f / sqrtf(s / static_cast<float>(dv) + eps);
-  const T* gr = gate + static_cast<long long>(t) * gate_ld + h * dv;
+  const T* gr = gate ? gate + static_cast<long long>(t) * gate_ld + h * dv : nullptr;
   T* dst = out + static_cast<long long>(t) * out_ld + h * dv;
-  for (int c = lane; c < dv; c += 32) dst[c] = from_f<T>(orow[c] * inv * w[h * w_stride + c] * sigmoidf_(to_f(gr[c])) * mult);
+  for (int c = lane; c < dv; c += 32) dst[c] = from_f<T>(orow[c] * inv * w[h * w_stride + c] * (gr ? sigmoidf_(to_f(gr[c])) : 1.f) * mult);
 }
 
 }  // namespace recur
@@ -903,9 +1019,43 @@ DSB_EXPORT int dsb200_delta_rule_scan(const float* qn, const float* kn, const fl
   return DSB_OK;
 }
 
+// Linear attention with the forget gate tied to the write strength, per sequence and head over the new tokens in order:
+//   q = silu(proj[q_col0 ..]),  f = lower + (1 - lower) sigmoid(proj[f_col0 ..] + f_bias),  S <- diag(f) S + (1 - f) v^T,  out = S^T q
+// proj [T, ld] (dtype 0 = bf16, 1 = fp32) with H heads of d (queries, gates) and dv (values); f_bias, lower fp32 [H d]; out fp32 [T, H dv];
+// state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros.
+DSB_EXPORT int dsb200_tied_gate_scan(const void* proj, long long ld, int q_col0, int f_col0, int v_col0, const float* f_bias, const float* lower,
+                                     const int* seq_desc, float* state_S, float* out, int n_seqs, int H, int d, int dv, int dtype,
+                                     cudaStream_t stream) {
+  if (n_seqs == 0) return DSB_OK;
+  int R, RPT, tiles, ch;
+  DSB_REQUIRE(scan_shape(d, dv, &R, &RPT, &tiles, &ch), "tied_gate_scan: a %d x %d state per head is not supported", d, dv);
+  const size_t smem = 2 * static_cast<size_t>(2 * ch * R * RPT + ch * SCAN_CPT * (SCAN_THREADS / R)) * sizeof(float);
+  DSB_REQUIRE(smem <= 200 * 1024, "tied_gate_scan: head sizes %d / %d do not fit shared memory", d, dv);
+  const dim3 grid(n_seqs, H, tiles);
+  bool launched = false;
+#define CALL_T(T, RPTv, Rv)                                                                                                                  \
+  do {                                                                                                                                       \
+    if (smem > 48 * 1024)                                                                                                                    \
+      DSB_CHECK_CUDA(cudaFuncSetAttribute(tied_gate_scan_kernel<T, RPTv, Rv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
+    tied_gate_scan_kernel<T, RPTv, Rv><<<grid, SCAN_THREADS, smem, stream>>>((const T*)proj, ld, q_col0, f_col0, v_col0, f_bias, lower,      \
+                                                                             (const int4*)seq_desc, state_S, out, H, d, dv, ch);             \
+  } while (0)
+#define CALL(RPTv, Rv)                     \
+  do {                                     \
+    if (dtype == 0) CALL_T(bf16, RPTv, Rv); \
+    else CALL_T(float, RPTv, Rv);          \
+  } while (0)
+  SCAN_DISPATCH_ALL(CALL);
+#undef CALL
+#undef CALL_T
+  DSB_REQUIRE(launched, "tied_gate_scan: no kernel for %d rows per thread x %d lanes", RPT, R);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
 // out[t, h dv + c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult.  o fp32
 // [T, H dv]; w fp32 (w_stride = dv: one weight row per head, 0: one row shared by the heads); gate [T, gate_ld] and out [T, out_ld] in the
-// activation dtype (0 = bf16, 1 = fp32).
+// activation dtype (0 = bf16, 1 = fp32).  gate may be null: mixers without an output gate.
 DSB_EXPORT int dsb200_head_norm_gate(const float* o, const float* w, int w_stride, const void* gate, long long gate_ld, void* out, long long out_ld,
                                      int n_tokens, int H, int dv, float eps, float mult, int dtype, cudaStream_t stream) {
   const long long warps = static_cast<long long>(n_tokens) * H;

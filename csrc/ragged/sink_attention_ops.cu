@@ -1,0 +1,255 @@
+// build: precise-math
+// Ragged-batch kernels for attention mixers whose heads are normed one by one and whose softmax has a sink:
+//
+//   head_norm_rotary_append   per token, from the fused projection: every query and key head is RMS-normed over its own entries with a weight
+//                             shared by the heads, then the first rot_dims entries of the head are rotated (entry i paired with entry
+//                             i + rot_dims / 2) by pos * freq[i], cosine and sine times a constant; every value head is divided by its own
+//                             root mean square (no weight).  Queries leave as a tensor, keys and values go to their rows of the paged cache.
+//   sink_attention            causal attention over the paged cache on CUDA cores: score = scale q . k, optionally soft-capped
+//                             (cap tanh(score / cap)); weights exp(s_j) / (sink + sum_j exp(s_j)) with sink = 1 for a softmax that has
+//                             one more, valueless entry of score 0, or 0 for the plain softmax.  Key and value heads may differ in size.
+//
+// Keys and values live in planes with their own row widths: k_cache + block * k_block_stride addresses block_size rows of G d values,
+// v_cache + block * v_block_stride block_size rows of G dv values (both planes of one [blocks, 2, block_size, G, d] cache when d = dv, or
+// two single-plane caches).  Every kernel takes its sizes as arguments and exists for bf16 and fp32 activations; norms, angles, scores and
+// softmax are fp32 (angles are formed and reduced in double).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "../common/host.h"
+
+namespace dsb {
+namespace sinkattn {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// One warp per (token, head slot); the H query heads, then the G key heads, then the G value heads of the token.
+template <typename T>
+__global__ void head_norm_rotary_append_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, int v_col0,
+                                               const float* __restrict__ wq, const float* __restrict__ wk, const double* __restrict__ freq,
+                                               float mag, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                               const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ k_cache,
+                                               long long k_block_stride, T* __restrict__ v_cache, long long v_block_stride, T* __restrict__ q_out,
+                                               long long q_ld, int n_tokens, int H, int G, int d, int dv, int rot, float eps, int norm_v) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int per_tok = H + 2 * G;
+  if (gw >= n_tokens * per_tok) return;
+  const int t = gw / per_tok, slot = gw % per_tok;
+  const int pos = tok_pos[t];
+  const T* row = proj + static_cast<long long>(t) * ld;
+  long long cache_row = 0;
+  if (slot >= H) cache_row = block_table[static_cast<size_t>(tok_seq[t]) * bt_stride + pos / block_size];
+  const int in_block = pos % block_size;
+  if (slot >= H + G) {  // a value head: its own root mean square, no weight
+    const int g = slot - H - G;
+    const T* src = row + v_col0 + g * dv;
+    T* dst = v_cache + cache_row * v_block_stride + (static_cast<long long>(in_block) * G + g) * dv;
+    float inv = 1.f;
+    if (norm_v) {
+      float s = 0.f;
+      for (int c = lane; c < dv; c += 32) { const float v = to_f(src[c]); s += v * v; }
+      s = warp_sum(s);
+      inv = 1.f / sqrtf(s / static_cast<float>(dv) + eps);
+    }
+    for (int c = lane; c < dv; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv);
+    return;
+  }
+  const bool is_q = slot < H;
+  const int head = is_q ? slot : slot - H;
+  const T* src = row + (is_q ? q_col0 : k_col0) + head * d;
+  const float* w = is_q ? wq : wk;
+  T* dst = is_q ? q_out + static_cast<long long>(t) * q_ld + head * d
+                : k_cache + cache_row * k_block_stride + (static_cast<long long>(in_block) * G + head) * d;
+  float inv = 1.f;
+  if (w != nullptr) {
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = to_f(src[c]); s += v * v; }
+    s = warp_sum(s);
+    inv = 1.f / sqrtf(s / static_cast<float>(d) + eps);
+  }
+  const int half = rot >> 1;
+  for (int i = lane; i < half; i += 32) {
+    const float u = to_f(src[i]) * inv * (w ? w[i] : 1.f), v = to_f(src[i + half]) * inv * (w ? w[i + half] : 1.f);
+    double a = static_cast<double>(pos) * freq[i];
+    a -= 6.283185307179586476925 * rint(a * 0.15915494309189533576888);  // into [-pi, pi] before single precision takes over
+    float sn, cs;
+    sincosf(static_cast<float>(a), &sn, &cs);
+    sn *= mag;
+    cs *= mag;
+    dst[i] = from_f<T>(u * cs - v * sn);
+    dst[i + half] = from_f<T>(v * cs + u * sn);
+  }
+  for (int c = rot + lane; c < d; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv * (w ? w[c] : 1.f));
+}
+
+// One block per (token, query head).  The visible keys 0 .. pos are walked in chunks of SA_CHUNK with a running maximum / sum (fp32).
+constexpr int SA_CHUNK = 256, SA_THREADS = 128;
+template <typename T>
+__global__ void __launch_bounds__(SA_THREADS)
+sink_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __restrict__ k_cache, long long k_block_stride,
+                      const T* __restrict__ v_cache, long long v_block_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                      const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ out, long long out_ld, int H, int G,
+                      int d, int dv, float scale, float cap, float sink) {
+  extern __shared__ float sm[];
+  __shared__ float red[33];
+  __shared__ float sc[SA_CHUNK];
+  __shared__ int key_blk[SA_CHUNK], key_slot[SA_CHUNK];
+  const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  float* qs = sm;        // [d]
+  float* acc = sm + d;   // [dv]
+  for (int c = threadIdx.x; c < d; c += SA_THREADS) qs[c] = to_f(q[static_cast<long long>(t) * q_ld + h * d + c]) * scale;
+  for (int c = threadIdx.x; c < dv; c += SA_THREADS) acc[c] = 0.f;
+  const int n = pos + 1;
+  const int* bt = block_table + static_cast<size_t>(seq) * bt_stride;
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  __syncthreads();
+  for (int x0 = 0; x0 < n; x0 += SA_CHUNK) {
+    const int cn = min(SA_CHUNK, n - x0);
+    float mx = -INFINITY;
+    for (int x = threadIdx.x; x < cn; x += SA_THREADS) {
+      const int j = x0 + x;
+      const int blk = bt[j / block_size], slot = j % block_size;
+      key_blk[x] = blk;
+      key_slot[x] = slot;
+      const T* kr = k_cache + static_cast<long long>(blk) * k_block_stride + (static_cast<long long>(slot) * G + g) * d;
+      float s = 0.f;
+      for (int c = 0; c < d; ++c) s = fmaf(qs[c], to_f(kr[c]), s);
+      if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+      sc[x] = s;
+      mx = fmaxf(mx, s);
+    }
+    mx = block_max(mx, red);
+    const float m_new = fmaxf(m_run, mx);
+    float ls = 0.f;
+    for (int x = threadIdx.x; x < cn; x += SA_THREADS) {
+      const float p = expf(sc[x] - m_new);
+      sc[x] = p;
+      ls += p;
+    }
+    ls = block_sum(ls, red);
+    const float corr = expf(m_run - m_new);  // 0 for the first chunk (m_run = -inf)
+    l_run = l_run * corr + ls;
+    m_run = m_new;
+    for (int c = threadIdx.x; c < dv; c += SA_THREADS) {
+      float a = acc[c] * corr;
+      for (int x = 0; x < cn; ++x)
+        a = fmaf(sc[x], to_f(v_cache[static_cast<long long>(key_blk[x]) * v_block_stride + (static_cast<long long>(key_slot[x]) * G + g) * dv + c]), a);
+      acc[c] = a;
+    }
+    __syncthreads();
+  }
+  const float inv = 1.f / (l_run + sink * expf(-m_run));  // the sink's score is 0: exp(0 - m) in the shifted sum
+  for (int c = threadIdx.x; c < dv; c += SA_THREADS) out[static_cast<long long>(t) * out_ld + h * dv + c] = from_f<T>(acc[c] * inv);
+}
+
+}  // namespace sinkattn
+}  // namespace dsb
+
+using namespace dsb;
+using namespace dsb::sinkattn;
+
+// proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds per token the query heads [H d] at q_col0, the key heads [G d] at k_col0 and the value heads
+// [G dv] at v_col0.  Query / key heads: RMS norm over d with the weights wq / wk [d] (shared by the heads; null = no norm), then rotation
+// of the first rot_dims entries (pairs (i, i + rot_dims / 2)) by pos * freq[i] (freq: rot_dims / 2 doubles on the device) with cosine and
+// sine multiplied by `mag`.  Value heads: divided by their root mean square over dv when norm_v.  Queries -> q_out [T, q_ld]; keys ->
+// k_cache, values -> v_cache at the token's (block, slot) (see the file header for the plane addressing).
+DSB_EXPORT int dsb200_head_norm_rotary_append(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* wq, const float* wk,
+                                              const double* freq, float mag, const int* tok_seq, const int* tok_pos, const int* block_table,
+                                              int bt_stride, int block_size, void* k_cache, long long k_block_stride, void* v_cache,
+                                              long long v_block_stride, void* q_out, long long q_ld, int n_tokens, int H, int G, int d, int dv,
+                                              int rot_dims, float eps, int norm_v, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H >= 1 && G >= 1 && d >= 1 && dv >= 1 && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || freq != nullptr),
+              "head_norm_rotary_append: heads %d / %d, head sizes %d / %d, rotated %d", H, G, d, dv, rot_dims);
+  const long long warps = static_cast<long long>(n_tokens) * (H + 2 * G);
+  const int wpb = 8;
+  const int grid = static_cast<int>((warps + wpb - 1) / wpb);
+  if (dtype == 0)
+    head_norm_rotary_append_kernel<bf16><<<grid, wpb * 32, 0, stream>>>((const bf16*)proj, ld, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok_seq, tok_pos,
+                                                                       block_table, bt_stride, block_size, (bf16*)k_cache, k_block_stride,
+                                                                       (bf16*)v_cache, v_block_stride, (bf16*)q_out, q_ld, n_tokens, H, G, d, dv,
+                                                                       rot_dims, eps, norm_v);
+  else
+    head_norm_rotary_append_kernel<float><<<grid, wpb * 32, 0, stream>>>((const float*)proj, ld, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok_seq,
+                                                                        tok_pos, block_table, bt_stride, block_size, (float*)k_cache, k_block_stride,
+                                                                        (float*)v_cache, v_block_stride, (float*)q_out, q_ld, n_tokens, H, G, d, dv,
+                                                                        rot_dims, eps, norm_v);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out[t, h dv + c] = sum_j p_j v_j[c] over the keys j <= pos(t) of the token's sequence, p_j = exp(s_j) / (sink + sum_j exp(s_j)),
+// s_j = scale q_h . k_j, soft-capped as cap tanh(s_j / cap) when cap > 0.  q [T, q_ld] (H heads of d); query head h reads key/value head
+// h / (H / G); out [T, out_ld] (H heads of dv).  CUDA cores, fp32 scores and accumulation, any sizes; dtype 0 = bf16, 1 = fp32.
+DSB_EXPORT int dsb200_sink_attention(const void* q, long long q_ld, const void* k_cache, long long k_block_stride, const void* v_cache,
+                                     long long v_block_stride, const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
+                                     int block_size, void* out, long long out_ld, int n_tokens, int H, int G, int d, int dv, float scale, float cap,
+                                     float sink, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && d >= 1 && dv >= 1 && d + dv <= 8192 && sink >= 0.f, "sink_attention: heads %d / %d, head sizes %d / %d", H, G,
+              d, dv);
+  const dim3 grid(n_tokens, H);
+  const size_t smem = static_cast<size_t>(d + dv) * sizeof(float);
+  if (dtype == 0)
+    sink_attention_kernel<bf16><<<grid, SA_THREADS, smem, stream>>>((const bf16*)q, q_ld, (const bf16*)k_cache, k_block_stride, (const bf16*)v_cache,
+                                                                    v_block_stride, tok_seq, tok_pos, block_table, bt_stride, block_size, (bf16*)out,
+                                                                    out_ld, H, G, d, dv, scale, cap, sink);
+  else
+    sink_attention_kernel<float><<<grid, SA_THREADS, smem, stream>>>((const float*)q, q_ld, (const float*)k_cache, k_block_stride,
+                                                                     (const float*)v_cache, v_block_stride, tok_seq, tok_pos, block_table, bt_stride,
+                                                                     block_size, (float*)out, out_ld, H, G, d, dv, scale, cap, sink);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}

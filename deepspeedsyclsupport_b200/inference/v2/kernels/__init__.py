@@ -226,7 +226,8 @@ def moe_gather(moe_out, scores, mapped_slots):
 # ---- kernels of csrc/ragged/latent_ops.cu: fp32 residual stream, latent-cache attention, grouped top-k router, expert MLP pieces
 # for any width in bf16 or fp32.  Device only: these ops have no host form (their oracles live with the tests).
 native.register_sigs({
-    "dsb200_embed_sinusoid": "pp i pp p ii p",
+    "dsb200_embed_sinusoid": "pp i pp p ii f p",
+    "dsb200_stream_group_norm": "ppp i pp p i pp iii f p",
     "dsb200_sandwich_norm": "pp i p ff p f p i pp ii f i p",
     "dsb200_latent_norm_append": "p i pp pp ppp iiii ii f i p",
     "dsb200_paged_flash_latent": "p i ll pp ppp iiiiii f ii p i p",
@@ -235,10 +236,11 @@ native.register_sigs({
     "dsb200_latent_attention": "p i ll p i p ll p ppp ii iii f i p",
     "dsb200_sigmoid_gate_mul": "p l p l l i i p",
     "dsb200_clamped_swish_gate": "pp l i fff i p",
+    "dsb200_clamped_swish_gate_cols": "p l ii p l l i fff i p",
     "dsb200_softcap": "p l l i f p",
     "dsb200_grouped_topk_gating": "pppppp iiiiiii p",
     "dsb200_moe_scatter_rows": "ppppppp iiii i p p",
-    "dsb200_moe_gather_rows": "pppp iii i p",
+    "dsb200_moe_gather_rows": "pppp iii i p i p p",
     "dsb200_moe_gemm_rows": "pppp iiii i p",
 }, restype_long=("dsb200_latent_attention_scratch_floats", ))
 
@@ -257,12 +259,33 @@ def sinusoid_frequencies(dim, base=10000.0, device=None):
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dim).to(device)
 
 
-def embed_sinusoid(ids, table, tok_pos, freq):
-    """fp32 [T, dim]: table[ids] + (sin(p f_0), cos(p f_0), sin(p f_1), ...); `freq` None: the table rows alone."""
+def embed_sinusoid(ids, table, tok_pos, freq, scale=1.0):
+    """fp32 [T, dim]: scale * table[ids] + (sin(p f_0), cos(p f_0), sin(p f_1), ...); `freq` None: the scaled table rows alone."""
     T, dim = ids.numel(), table.shape[1]
     out = torch.empty(T, dim, dtype=torch.float32, device=table.device)
     native.check(native.lib().dsb200_embed_sinusoid(native.ptr(ids), native.ptr(table), _dt(table), native.ptr(tok_pos), native.ptr(freq),
-                                                    native.ptr(out), T, dim, native.stream_ptr()))
+                                                    native.ptr(out), T, dim, float(scale), native.stream_ptr()))
+    return out
+
+
+def stream_group_norm(x, branches=(), branch_fp32=None, w=None, groups=1, eps=1e-6, out_dtype=torch.bfloat16, rows=None, fp32_copy=False):
+    """On the fp32 residual x [T, dim], in place: x += every tensor of `branches` (at most two, in one activation dtype) + branch_fp32
+    (fp32).  With w: returns x normed in `groups` equal consecutive parts (each divided by its own root mean square, eps inside the root)
+    times w, in `out_dtype`; with `fp32_copy` -> (out, the same values before rounding).  `rows` (int32 indices): only those rows are summed
+    and normed, the result has one row per index and x itself is left as it was."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.is_cuda and len(branches) <= 2
+    ys = [y if y.is_contiguous() else y.contiguous() for y in branches]
+    assert all(y.shape == x.shape and y.dtype == ys[0].dtype for y in ys)
+    assert branch_fp32 is None or (branch_fp32.shape == x.shape and branch_fp32.dtype == torch.float32 and branch_fp32.is_contiguous())
+    n = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device) if w is not None else None
+    out32 = torch.empty(n, x.shape[1], dtype=torch.float32, device=x.device) if (fp32_copy and w is not None and out_dtype != torch.float32) else None
+    ys += [None] * (2 - len(ys))
+    native.check(native.lib().dsb200_stream_group_norm(native.ptr(x), native.ptr(ys[0]), native.ptr(ys[1]), _dt(ys[0]) if ys[0] is not None else 0,
+                                                       native.ptr(branch_fp32), native.ptr(w), native.ptr(out), _DT[out_dtype], native.ptr(out32),
+                                                       native.ptr(rows), n, x.shape[1], int(groups), float(eps), native.stream_ptr()))
+    if fp32_copy:
+        return out, (out32 if out32 is not None else out)
     return out
 
 
@@ -388,6 +411,15 @@ def clamped_swish_gate(gu, alpha, limit, shift):
     return out
 
 
+def clamped_swish_gate_cols(gu, gate_col0, up_col0, F, out, alpha, limit, shift):
+    """`clamped_swish_gate` on column ranges: gate = gu[:, gate_col0 : gate_col0 + F], up = gu[:, up_col0 : up_col0 + F] of a fused projection,
+    result into `out` [rows, F] (a view with unit column stride, e.g. a column range of the next GEMM's input)."""
+    assert gu.stride(1) == 1 and out.stride(1) == 1 and out.shape == (gu.shape[0], F) and gu.dtype == out.dtype
+    native.check(native.lib().dsb200_clamped_swish_gate_cols(native.ptr(gu), gu.stride(0), int(gate_col0), int(up_col0), native.ptr(out), out.stride(0),
+                                                             gu.shape[0], int(F), float(alpha), float(limit), float(shift), _dt(gu), native.stream_ptr()))
+    return out
+
+
 def softcap_(logits, cap):
     """logits <- cap * tanh(logits / cap), in place on an fp32 [rows, cols] view."""
     assert logits.dtype == torch.float32 and logits.is_cuda and logits.stride(1) == 1
@@ -426,13 +458,17 @@ def moe_scatter_rows(x, counts, assignments, offsets, row_scale=None):
     return moe_in, cumsum, slots
 
 
-def moe_gather_rows(moe_out, scores, mapped_slots):
-    """fp32 [T, dim]: sum_k scores[t, k] * moe_out[mapped_slots[t, k]] (`scores` None: the plain sum)."""
+def moe_gather_rows(moe_out, scores, mapped_slots, assignments=None, n_real=0, identity_src=None):
+    """fp32 [T, dim]: sum_k scores[t, k] * moe_out[mapped_slots[t, k]] (`scores` None: the plain sum).  With `assignments` [T, k]: experts
+    `n_real` and above are identity experts -- their output is the token's row of `identity_src` (fp32 [T, dim])."""
     T, k = mapped_slots.shape
     assert moe_out.is_contiguous()
+    if assignments is not None:
+        assert identity_src is not None and identity_src.dtype == torch.float32 and identity_src.is_contiguous() and identity_src.shape == (T, moe_out.shape[1])
     out = torch.empty(T, moe_out.shape[1], dtype=torch.float32, device=moe_out.device)
     native.check(native.lib().dsb200_moe_gather_rows(native.ptr(moe_out), native.ptr(scores), native.ptr(mapped_slots), native.ptr(out), T,
-                                                     moe_out.shape[1], k, _dt(moe_out), native.stream_ptr()))
+                                                     moe_out.shape[1], k, _dt(moe_out), native.ptr(assignments), int(n_real),
+                                                     native.ptr(identity_src), native.stream_ptr()))
     return out
 
 
@@ -460,6 +496,9 @@ native.register_sigs({
     "dsb200_delta_prepare": "p l iii ppp p pp ppp pppp iiiiii i p",
     "dsb200_delta_rule_scan": "ppppp p pp iiiii p",
     "dsb200_head_norm_gate": "pp i p l p l iii ff i p",
+    "dsb200_tied_gate_scan": "p l iii pp p pp iiii i p",
+    "dsb200_head_norm_rotary_append": "p l iii pp p f ppp ii p l p l p l iiiii i f i i p",
+    "dsb200_sink_attention": "p l p l p l ppp ii p l iiiii fff i p",
 }, restype_long=("dsb200_scan_state_floats", ))
 
 
@@ -582,10 +621,66 @@ def delta_rule_scan(qn, kn, v, beta, decay, seq_desc, n_seqs, state_S, H, G, d, 
 
 def head_norm_gate(o, w, gate, out, H, dv, eps, mult=1.0, shared_weight=False):
     """out[:, h dv + c] = rms_norm_over_c(o[:, h, :]) * w * sigmoid(gate) * mult; o fp32 [T, H dv]; w fp32 [H dv] or (shared) [dv];
-    gate / out: views [T, >= H dv] of the activation dtype with unit column stride."""
+    gate / out: views [T, >= H dv] of the activation dtype with unit column stride; gate None: no gate factor."""
     T = o.shape[0]
-    assert o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and out.stride(1) == 1 and gate.dtype == out.dtype
-    native.check(native.lib().dsb200_head_norm_gate(native.ptr(o), native.ptr(w), 0 if shared_weight else dv, native.ptr(gate), gate.stride(0),
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.stride(1) == 1
+    assert gate is None or (gate.stride(1) == 1 and gate.dtype == out.dtype)
+    native.check(native.lib().dsb200_head_norm_gate(native.ptr(o), native.ptr(w), 0 if shared_weight else dv, native.ptr(gate),
+                                                    gate.stride(0) if gate is not None else 0,
                                                     native.ptr(out), out.stride(0), T, H, dv, float(eps), float(mult), _dt(out),
                                                     native.stream_ptr()))
+    return out
+
+
+def tied_gate_scan(proj, q_col0, f_col0, v_col0, f_bias, lower, seq_desc, n_seqs, state_S, H, d, dv):
+    """Linear attention whose forget gate also sets the write strength, over every sequence's new tokens -> fp32 [T, H dv] read-outs:
+    q = silu(proj[:, q_col0:]), f = lower + (1 - lower) sigmoid(proj[:, f_col0:] + f_bias), S <- diag(f) S + (1 - f) v^T, o = S^T q."""
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and f_bias.dtype == torch.float32 and lower.dtype == torch.float32 and f_bias.numel() == H * d == lower.numel()
+    out = torch.empty(T, H * dv, dtype=torch.float32, device=proj.device)
+    native.check(native.lib().dsb200_tied_gate_scan(native.ptr(proj), proj.stride(0), q_col0, f_col0, v_col0, native.ptr(f_bias), native.ptr(lower),
+                                                    native.ptr(seq_desc), native.ptr(state_S), native.ptr(out), n_seqs, H, d, dv, _dt(proj),
+                                                    native.stream_ptr()))
+    return out
+
+
+# ---- kernels of csrc/ragged/sink_attention_ops.cu: per-head query / key norms with a partial rotate-half rotation, weightless value norm,
+# and causal attention with a soft cap on the scores and a sink in the softmax.  Keys and values are addressed as planes
+# (tensor, elements between consecutive blocks): `cache_planes` turns the engine's cache tensors into that form.
+def cache_planes(k_cache, v_cache=None):
+    """((keys, block stride), (values, block stride)).  One tensor [blocks, 2, block_size, G, d] holds both planes (d = dv); two tensors
+    [blocks, block_size, G, d] and [blocks, block_size, G, dv] hold one each."""
+    if v_cache is None:
+        assert k_cache.dim() == 5 and k_cache.shape[1] == 2 and k_cache.is_contiguous()
+        return (k_cache, k_cache.stride(0)), (k_cache[:, 1], k_cache.stride(0))
+    assert k_cache.dim() == 4 and v_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    return (k_cache, k_cache.stride(0)), (v_cache, v_cache.stride(0))
+
+
+def head_norm_rotary_append(proj, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok_seq, tok_pos, block_table, block_size, k_plane, v_plane, q_out,
+                            H, G, d, dv, rot_dims, eps, norm_v=True):
+    """Per-head RMS norm (weights wq / wk [d], shared by the heads) and rotation of the first rot_dims entries (entry i with entry
+    i + rot_dims / 2, angle pos * freq[i], cosine and sine times `mag`) of the query / key heads in columns q_col0 / k_col0 of proj; value
+    heads (columns v_col0) divided by their own root mean square when `norm_v`.  Queries -> q_out [T, >= H d]; keys / values -> their planes."""
+    T = proj.shape[0]
+    (kc, ks), (vc, vs) = k_plane, v_plane
+    assert proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.dtype == proj.dtype == kc.dtype == vc.dtype
+    native.check(native.lib().dsb200_head_norm_rotary_append(native.ptr(proj), proj.stride(0), q_col0, k_col0, v_col0, native.ptr(wq), native.ptr(wk),
+                                                             native.ptr(freq), float(mag), native.ptr(tok_seq), native.ptr(tok_pos),
+                                                             native.ptr(block_table), block_table.stride(0), int(block_size), native.ptr(kc), ks,
+                                                             native.ptr(vc), vs, native.ptr(q_out), q_out.stride(0), T, H, G, d, dv, int(rot_dims),
+                                                             float(eps), int(norm_v), _dt(proj), native.stream_ptr()))
+    return q_out
+
+
+def sink_attention(q, k_plane, v_plane, tok_seq, tok_pos, block_table, block_size, out, H, G, d, dv, scale, softcap=0.0, sink=1.0):
+    """CUDA-core causal attention over the paged planes: weights exp(s_j) / (sink + sum exp(s_j)) with s_j = scale q . k_j, soft-capped
+    as softcap tanh(s_j / softcap) when softcap > 0.  q [T, >= H d], out [T, >= H dv] (views with unit column stride)."""
+    T = q.shape[0]
+    (kc, ks), (vc, vs) = k_plane, v_plane
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == kc.dtype == vc.dtype == out.dtype
+    native.check(native.lib().dsb200_sink_attention(native.ptr(q), q.stride(0), native.ptr(kc), ks, native.ptr(vc), vs, native.ptr(tok_seq),
+                                                    native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0), int(block_size),
+                                                    native.ptr(out), out.stride(0), T, H, G, d, dv, float(scale), float(softcap), float(sink),
+                                                    _dt(q), native.stream_ptr()))
     return out

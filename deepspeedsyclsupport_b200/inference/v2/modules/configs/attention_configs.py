@@ -128,3 +128,53 @@ class DSWindowedAttentionConfig(DSModuleConfig):
     @property
     def group_size(self) -> int:
         return self.n_heads_q // self.n_heads_kv
+
+
+class RampRotaryScalingConfig(DeepSpeedConfigModel):
+    """Frequency scaling with a linear ramp over the channel index: with c(t) = dims ln(original / (2 pi t)) / (2 ln base) the channel that
+    makes t turns over `original` positions, lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)), dims - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), channel i turns at f_i / factor * ramp_i + f_i (1 - ramp_i); cosine and sine are
+    multiplied by 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+class DSSinkAttentionConfig(DSModuleConfig):
+    """Causal attention with per-head query / key RMS norms (one weight of head size shared by the heads, applied before the rotation), a
+    rotate-half rotation of the first `rotate_dim` entries of a head, values divided by their own root mean square (no weight; cached so),
+    scores scale * q . k soft-capped as softcap tanh(. / softcap), and a softmax whose denominator has `sink` added (1: one more entry of
+    score 0 without a value).  Query / key heads have `head_size` entries, value heads `value_size`."""
+    n_heads_q: int
+    n_heads_kv: int
+    head_size: int
+    value_size: int
+    scale: float  # softmax scale (given, not derived from the head size)
+    softcap: float = 0.0  # 0 = no cap
+    sink: float = 1.0
+    qk_norm: bool = True
+    v_norm: bool = True
+    rotate_dim: int = 0
+    theta_base: float = 10_000.0
+    rotary_scaling: Optional[RampRotaryScalingConfig] = None
+    eps: float = 1e-6
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16
+
+    @model_validator(mode="after")
+    def _consistent(self):
+        if self.n_heads_q <= 0 or self.n_heads_kv <= 0 or self.n_heads_q % self.n_heads_kv != 0:
+            raise ValueError(f"n_heads_q ({self.n_heads_q}) must be a positive multiple of n_heads_kv ({self.n_heads_kv})")
+        if self.head_size <= 0 or self.value_size <= 0:
+            raise ValueError("head sizes must be positive")
+        if not (0 <= self.rotate_dim <= self.head_size and self.rotate_dim % 2 == 0):
+            raise ValueError(f"rotate_dim must be even and at most head_size ({self.head_size}), got {self.rotate_dim}")
+        if self.softcap < 0 or self.sink < 0:
+            raise ValueError("softcap and sink cannot be negative")
+        return self
+
+    @property
+    def group_size(self) -> int:
+        return self.n_heads_q // self.n_heads_kv

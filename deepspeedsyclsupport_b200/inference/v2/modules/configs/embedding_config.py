@@ -17,3 +17,5 @@ class DSEmbeddingsConfig(DSModuleConfig):
     sinusoidal_base: Optional[float] = None
     # the embedding leaves as the fp32 start of a residual stream whatever the table's dtype (implied by sinusoidal_base)
     fp32_stream: bool = False
+    # the table row is multiplied by this (in fp32) on its way into an fp32 stream
+    embedding_scale: float = 1.0

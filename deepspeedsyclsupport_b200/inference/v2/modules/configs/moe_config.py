@@ -26,3 +26,6 @@ class DSMoEConfig(DSModuleConfig):
     act_alpha: float = 1.702
     act_limit: float = 7.0
     act_shift: float = 1.0
+    # identity experts: the router has n_experts + n_identity_experts outputs; the last n_identity_experts of them have no weights and
+    # return their input (times the routing weight)
+    n_identity_experts: int = 0

@@ -21,6 +21,11 @@ class DSNormConfig(DSModuleConfig):
     sandwich: bool = False
     # sandwich blocks only: the normed branch is multiplied by this before it joins the stream (x += branch_mult * norm(branch) * ...)
     branch_mult: float = 1.0
+    # "shared input" blocks: ONE norm per layer whose output every sublayer of the layer reads; the sublayers' outputs join the fp32 stream as
+    # a plain sum in the pass that forms the next layer's norm.  The row is normed in `groups` equal consecutive parts, each divided by its
+    # own root mean square, before the weight is applied.
+    shared_input: bool = False
+    groups: int = 1
 
     @field_validator("channels")
     @classmethod

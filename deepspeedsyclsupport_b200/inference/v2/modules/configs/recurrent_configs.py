@@ -32,3 +32,17 @@ class DSDeltaRuleConfig(DSModuleConfig):
     max_sequences: int
     input_dtype: DtypeEnum = DtypeEnum.bf16
     output_dtype: DtypeEnum = DtypeEnum.bf16
+
+
+class DSTiedGateConfig(DSModuleConfig):
+    """Linear attention whose forget gate also decides what is written (there is no key projection): per head, q = silu(W_q h),
+    f = lower + (1 - lower) sigmoid(W_f h + b) per key channel, S <- diag(f) S + (1 - f) v^T, o = S^T q; the read-out gets a per-head RMS norm
+    with a weight shared by the heads (no output gate)."""
+    n_heads: int
+    key_size: int
+    value_size: int
+    eps: float = 1e-6
+    out_scale: float = 1.0
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16

@@ -5,7 +5,7 @@ from ..config_v2 import RaggedInferenceEngineConfig
 from ..inference_utils import ActivationType, NormTypeEnum
 from . import implementations  # noqa: F401  (registers the implementations)
 from .configs import (DSDeltaRuleConfig, DSEmbeddingsConfig, DSLatentAttentionConfig, DSLinearConfig, DSMatrixMemoryConfig, DSMoEConfig, DSNormConfig,
-                      DSSelfAttentionConfig, DSUnembedConfig, DSWindowedAttentionConfig)
+                      DSSelfAttentionConfig, DSSinkAttentionConfig, DSTiedGateConfig, DSUnembedConfig, DSWindowedAttentionConfig)
 from .interfaces import (DSEmbeddingBase, DSEmbeddingRegistry, DSLinearBase, DSLinearRegistry, DSMoEBase, DSMoERegistry, DSPostNormBase,
                          DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry, DSRecurrentMixerBase, DSRecurrentRegistry, DSSelfAttentionBase,
                          DSSelfAttentionRegistry, DSUnembedBase, DSUnembedRegistry)
@@ -22,12 +22,14 @@ def instantiate_attention(attention_config, engine_config: RaggedInferenceEngine
         return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="latent_blocked_attention", config=attention_config))
     if isinstance(attention_config, DSWindowedAttentionConfig):  # convolved q / k, values = keys, sliding window that keeps the first tokens
         return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="windowed_conv_attention", config=attention_config))
+    if isinstance(attention_config, DSSinkAttentionConfig):  # per-head q / k / v norms, soft-capped scores, a sink in the softmax
+        return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="sink_blocked_attention", config=attention_config))
     return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="dense_blocked_attention", config=attention_config))
 
 
 def instantiate_recurrent(mixer_config, engine_config: RaggedInferenceEngineConfig = None) -> DSRecurrentMixerBase:
     """Token mixers with a fixed-size state per sequence; the config class names the recurrence."""
-    name = {DSMatrixMemoryConfig: "matrix_memory", DSDeltaRuleConfig: "channel_delta_rule"}[type(mixer_config)]
+    name = {DSMatrixMemoryConfig: "matrix_memory", DSDeltaRuleConfig: "channel_delta_rule", DSTiedGateConfig: "tied_gate_linear"}[type(mixer_config)]
     return DSRecurrentRegistry.instantiate_config(ConfigBundle(name=name, config=mixer_config))
 
 
@@ -50,7 +52,7 @@ def instantiate_linear(linear_config: DSLinearConfig, engine_config: RaggedInfer
 
 def instantiate_moe(moe_config: DSMoEConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSMoEBase:
     if (moe_config.n_groups > 1 or moe_config.use_correction or ActivationType(moe_config.activation) == ActivationType.ClampedSwiGLU or
-            moe_config.score_function != "softmax" or moe_config.scale_input):
+            moe_config.score_function != "softmax" or moe_config.scale_input or moe_config.n_identity_experts > 0):
         return DSMoERegistry.instantiate_config(ConfigBundle(name="grouped_topk_moe", config=moe_config))
     bundle = ConfigBundle(name="cutlass_multi_gemm_moe", config=moe_config, implementation_config={"weight_dtype": moe_config.input_dtype})
     return DSMoERegistry.instantiate_config(bundle)
@@ -63,6 +65,8 @@ def instantiate_post_norm(norm_config: DSNormConfig, engine_config: RaggedInfere
 def instantiate_pre_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSPreNormBase:
     kind = NormTypeEnum(norm_config.type)
     name = "cuda_pre_ln" if kind == NormTypeEnum.LayerNorm else ("cuda_sandwich_rms" if norm_config.sandwich else "cuda_pre_rms")
+    if kind == NormTypeEnum.RMSNorm and norm_config.shared_input:
+        name = "cuda_group_rms"
     return DSPreNormRegistry.instantiate_config(ConfigBundle(name=name, config=norm_config))
 
 

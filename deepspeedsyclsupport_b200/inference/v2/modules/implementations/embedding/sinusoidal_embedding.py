@@ -1,4 +1,5 @@
-"""Token embedding, optionally plus a fixed sinusoidal position vector, written as the fp32 start of the residual stream.
+"""Token embedding (times an optional constant), optionally plus a fixed sinusoidal position vector, written as the fp32 start of the
+residual stream.
 
 Entry 2i of the position vector is sin(p * base^(-2i / dim)) and entry 2i + 1 the cosine of the same angle, p being the token's
 position in its sequence.  The angles are formed in double precision on the device (a position in the thousands times a
@@ -45,5 +46,5 @@ class DSSinusoidalEmbedding(DSEmbeddingBase):
         assert position_embeddings is None and token_type_ids is None
         if self._config.sinusoidal_base is not None and (self._freq is None or self._freq.device != word_embeddings.device):
             self._freq = K.sinusoid_frequencies(self._config.embedding_dim, self._config.sinusoidal_base, word_embeddings.device)
-        self._output = K.embed_sinusoid(ragged_batch.input_ids(), word_embeddings, ragged_batch.tok_pos(), self._freq)
+        self._output = K.embed_sinusoid(ragged_batch.input_ids(), word_embeddings, ragged_batch.tok_pos(), self._freq, scale=self._config.embedding_scale)
         return self._output

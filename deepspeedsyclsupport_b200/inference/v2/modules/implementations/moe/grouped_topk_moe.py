@@ -3,7 +3,8 @@
 Router (fp32): scores = softmax(W_r h) over all experts, or (`score_function` "sigmoid") the sigmoid of every logit on its own; the
 SELECTION uses scores + correction (when the config has one), restricted to the `keep_groups` contiguous expert groups whose best
 selection score is largest; the WEIGHTS are the plain scores of the chosen experts (optionally renormalised).  They multiply the
-experts' outputs in the combine or, with `scale_input`, the experts' inputs in the scatter (out = sum_k expert_k(s_k h)).  Experts: two
+experts' outputs in the combine or, with `scale_input`, the experts' inputs in the scatter (out = sum_k expert_k(s_k h)).  `n_identity_experts`: the router has that many outputs more than there are
+expert weights; a token that picks one of them gets its own input back, times the routing weight.  Experts: two
 grouped GEMMs over the rows sorted by expert with the gated activation between them (clamped swish, or plain silu(g) * u for SiGLU); the
 combine leaves in fp32 (it feeds an fp32 norm / residual).
 
@@ -35,8 +36,10 @@ class DSGroupedTopKMoE(DSMoEBase):
         if ActivationType(config.activation) not in (ActivationType.ClampedSwiGLU, ActivationType.SiGLU) or config.score_function not in ("softmax", "sigmoid"):
             return False
         g, k = config.n_groups, config.keep_groups
-        return (1 <= config.top_k <= min(config.n_experts, 32) and config.n_experts <= 2048 and g >= 1 and config.n_experts % g == 0 and
-                1 <= k <= g and k * (config.n_experts // g) >= config.top_k)
+        routed = config.n_experts + config.n_identity_experts  # router outputs: experts with weights, then identity experts
+        if config.n_identity_experts < 0 or (config.n_identity_experts and config.scale_input) or config.n_experts < 1:
+            return False
+        return (1 <= config.top_k <= min(routed, 32) and routed <= 2048 and g >= 1 and routed % g == 0 and 1 <= k <= g and k * (routed // g) >= config.top_k)
 
     def __init__(self, config: DSMoEConfig, implementation_config: Dict[str, Any] = None) -> None:
         super().__init__(config, implementation_config)
@@ -73,11 +76,18 @@ class DSGroupedTopKMoE(DSMoEBase):
         counts, scores, assignments, offsets = K.grouped_topk_gating(logits, c.top_k, correction, c.n_groups, c.keep_groups, c.normalize_scores,
                                                                      sigmoid_scores=c.score_function == "sigmoid")
         moe_in, cumsum, slots = K.moe_scatter_rows(hidden_states, counts, assignments, offsets, row_scale=scores if c.scale_input else None)
+        identity = None
+        if c.n_identity_experts:  # their rows sit behind the last real expert's in the sorted order: the GEMMs never touch them, the combine
+            cumsum = cumsum[:c.n_experts]  # reads the token's own (fp32) input instead
+            identity = router_input if router_input is not None else hidden_states.float()
         gu = self._grouped(moe_in, mlp_1_w, cumsum)
         if ActivationType(c.activation) == ActivationType.SiGLU:  # silu(g) * u: the clamped form without its limit and shift
             act = K.clamped_swish_gate(gu, 1.0, float("inf"), 0.0)
         else:
             act = K.clamped_swish_gate(gu, c.act_alpha, c.act_limit, c.act_shift)
         out = self._grouped(act, mlp_2_w, cumsum)
-        self._output = K.moe_gather_rows(out, None if c.scale_input else scores, slots)
+        if identity is not None:
+            self._output = K.moe_gather_rows(out, scores, slots, assignments=assignments, n_real=c.n_experts, identity_src=identity)
+        else:
+            self._output = K.moe_gather_rows(out, None if c.scale_input else scores, slots)
         return self._output

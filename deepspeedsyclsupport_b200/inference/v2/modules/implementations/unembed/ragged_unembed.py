@@ -33,13 +33,15 @@ class DSRaggedUnembed(DSUnembedBase):
 
     def forward(self, hidden_states: torch.Tensor, vocab_embedding: torch.Tensor, ragged_metadata, bias: Optional[torch.Tensor] = None,
                 gamma: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
-                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, pending=None) -> torch.Tensor:
         """`residual` (optional): the residual stream the last hidden state still has to be added to -- only the gathered rows
-        (one per sequence) are added and normalised, not the whole batch."""
+        (one per sequence) are added and normalised, not the whole batch.  `pending` (fp32 stream only): ((outputs in the activation
+        dtype, ...), fp32 output or None) of the last layer's sublayers that have not joined the stream yet; they are added to the
+        gathered rows only."""
         last_tok = ragged_metadata.logit_rows()
         c = self._config
         if c.residual_fp32:
-            return self._forward_fp32_residual(hidden_states, vocab_embedding, last_tok, gamma)
+            return self._forward_fp32_residual(hidden_states, vocab_embedding, last_tok, gamma, pending)
         h = K.logits_gather(hidden_states, last_tok)
         r = K.logits_gather(residual, last_tok) if residual is not None else None
         if self._norm == NormTypeEnum.RMSNorm:
@@ -61,7 +63,7 @@ class DSRaggedUnembed(DSUnembedBase):
         self._output = logits
         return logits
 
-    def _forward_fp32_residual(self, residual, vocab_embedding, rows, gamma):
+    def _forward_fp32_residual(self, residual, vocab_embedding, rows, gamma, pending=None):
         """Gather + RMS norm of the wanted rows in one kernel (fp32 in, activation dtype out), projection with fp32 logits,
         soft cap in place."""
         c = self._config
@@ -69,7 +71,12 @@ class DSRaggedUnembed(DSUnembedBase):
         act = DtypeEnum(c.dtype).value
         if rows.numel() == 0:
             return torch.empty(0, vocab_embedding.shape[0], dtype=torch.float32, device=residual.device)
-        h = K.sandwich_norm(residual, w=gamma, o=c.norm_weight_offset, eps=c.eps, out_dtype=act, rows=rows)
+        if c.norm_groups > 1 or pending is not None:  # the stream still lacks the last layer's outputs and / or is normed in parts
+            assert c.norm_weight_offset == 0.0
+            branches, fp32_branch = pending if pending is not None else ((), None)
+            h = K.stream_group_norm(residual, branches, fp32_branch, gamma, c.norm_groups, c.eps, out_dtype=act, rows=rows)
+        else:
+            h = K.sandwich_norm(residual, w=gamma, o=c.norm_weight_offset, eps=c.eps, out_dtype=act, rows=rows)
         logits = dense_matmul(h, vocab_embedding, out_dtype=torch.float32)
         if not logits.is_contiguous():
             logits = logits.contiguous()

@@ -379,9 +379,9 @@ int dsb200_fp8_rowwise_quantize(const void* x, void* q, float* scales, int rows,
 /* ---- csrc/ragged/latent_ops.cu */
 /* out[t, :] = table[ids[t], :] + sinusoid(tok_pos[t]): entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i); `freq` holds the
  * ceil(dim / 2) frequencies as doubles on the device, or is null for no position vector (tok_pos is then unused).
- * table_dtype: 0 = bf16, 1 = fp32.  out is fp32. */
+ * table_dtype: 0 = bf16, 1 = fp32.  out is fp32.  The table row is multiplied by `scale` (in fp32) before the position vector is added. */
 int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
-                          float* out, int n_tokens, int dim, dsb200_stream_t stream);
+                          float* out, int n_tokens, int dim, float scale, dsb200_stream_t stream);
 /* Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += y_mult * rms_norm(y) * (wb + ob); if w:
  * out = rms_norm(x) * (w + o); if plain_out (and no w): out = x.  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.
  * out32 (optional, fp32 [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32
@@ -389,6 +389,13 @@ int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dty
 int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, float y_mult, const float* w,
                          float o, void* out, int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps,
                          int plain_out, dsb200_stream_t stream);
+/* Output row r works on row src = rows[r] (src = r without `rows`) of the fp32 residual x and of the branches: x[src] + y0[src] + y1[src] +
+ * y2[src] (each branch optional; y0 and y1 in dtype y_dtype, y2 fp32) -- written back to x only without `rows` -- then, if w: out[r] = that
+ * row split into `groups` equal consecutive parts, each over its own root mean square (eps inside the root), times w.  out bf16
+ * (out_dtype 0) or fp32 (1); out32 (optional) the same values before rounding. */
+int dsb200_stream_group_norm(float* x, const void* y0, const void* y1, int y_dtype, const float* y2, const float* w,
+                             void* out, int out_dtype, float* out32, const int* rows, int n_rows, int dim, int groups,
+                             float eps, dsb200_stream_t stream);
 /* lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
  * of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, cache_ld] (cache_ld >= nkv:
  * rows may be padded to a width the tensor-core attention takes; the padding is never written). */
@@ -415,6 +422,11 @@ int dsb200_gate_heads(const void* a, const void* g, long long g_ld, void* out, i
 /* gu [rows, 2 F] = (gate | up) -> out [rows, F] = g' * sigmoid(alpha g') * (clamp(u, -limit, limit) + shift), g' = min(g, limit) */
 int dsb200_clamped_swish_gate(const void* gu, void* out, long long rows, int F, float alpha, float limit, float shift,
                               int dtype, dsb200_stream_t stream);
+/* out[r, c] = g' * sigmoid(alpha g') * (clamp(u, -limit, limit) + shift) with g' = min(gu[r, gate_col0 + c], limit), u = gu[r, up_col0 + c], c < F:
+ * gate and up are column ranges of one fused projection gu [rows, ld]; out [rows, out_ld] may be a column range of a wider buffer. */
+int dsb200_clamped_swish_gate_cols(const void* gu, long long ld, int gate_col0, int up_col0, void* out, long long out_ld,
+                                   long long rows, int F, float alpha, float limit, float shift, int dtype,
+                                   dsb200_stream_t stream);
 /* x[r, c] = cap * tanh(x[r, c] / cap) over fp32 [rows, cols] with row stride ld */
 int dsb200_softcap(float* x, long long ld, long long rows, int cols, float cap, dsb200_stream_t stream);
 /* Router: scores = softmax over the E logits of a token, or (sigmoid_scores) the sigmoid of every logit on its own; selection score =
@@ -431,9 +443,12 @@ int dsb200_grouped_topk_gating(const float* logits, const float* correction, int
 int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, const int* assignments, const int* offsets,
                             long long* expert_cumsum, void* moe_in, int* mapped_slots, int n_tokens, int n_experts,
                             int dim, int top_k, int dtype, const float* row_scale, dsb200_stream_t stream);
-/* out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]; scores may be null (plain sum) */
+/* out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]; scores may be null (plain sum).  With `assignments` (the chosen
+ * expert of every (token, k)): experts n_real and above are identity experts whose output is the token's row of identity_src (fp32
+ * [n_tokens, dim]) instead of a row of moe_out. */
 int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens,
-                           int dim, int top_k, int dtype, dsb200_stream_t stream);
+                           int dim, int top_k, int dtype, const int* assignments, int n_real, const float* identity_src,
+                           dsb200_stream_t stream);
 /* Grouped expert GEMM on CUDA cores: out[r, :] = w[expert(r)] x[r, :] for the R rows sorted by expert; x [R, K], w [E, N, K],
  * out [R, N], all bf16 (dtype 0) or all fp32 (dtype 1), contiguous; fp32 accumulation.  expert_cumsum [E] int64 on the device. */
 int dsb200_moe_gemm_rows(const void* x, const void* w, void* out, const long long* expert_cumsum, int R, int N, int K,
@@ -512,11 +527,39 @@ int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, int k_col0,
 int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay,
                            const int* seq_desc, float* state_S, float* out, int n_seqs, int H, int G, int d, int dv,
                            dsb200_stream_t stream);
+/* Linear attention with the forget gate tied to the write strength, per sequence and head over the new tokens in order:
+ *   q = silu(proj[q_col0 ..]),  f = lower + (1 - lower) sigmoid(proj[f_col0 ..] + f_bias),  S <- diag(f) S + (1 - f) v^T,  out = S^T q
+ * proj [T, ld] (dtype 0 = bf16, 1 = fp32) with H heads of d (queries, gates) and dv (values); f_bias, lower fp32 [H d]; out fp32 [T, H dv];
+ * state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros. */
+int dsb200_tied_gate_scan(const void* proj, long long ld, int q_col0, int f_col0, int v_col0, const float* f_bias,
+                          const float* lower, const int* seq_desc, float* state_S, float* out, int n_seqs, int H, int d,
+                          int dv, int dtype, dsb200_stream_t stream);
 /* out[t, h dv + c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult.  o fp32
  * [T, H dv]; w fp32 (w_stride = dv: one weight row per head, 0: one row shared by the heads); gate [T, gate_ld] and out [T, out_ld] in the
- * activation dtype (0 = bf16, 1 = fp32). */
+ * activation dtype (0 = bf16, 1 = fp32).  gate may be null: mixers without an output gate. */
 int dsb200_head_norm_gate(const float* o, const float* w, int w_stride, const void* gate, long long gate_ld, void* out,
                           long long out_ld, int n_tokens, int H, int dv, float eps, float mult, int dtype,
+                          dsb200_stream_t stream);
+
+/* ---- csrc/ragged/sink_attention_ops.cu */
+/* proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds per token the query heads [H d] at q_col0, the key heads [G d] at k_col0 and the value heads
+ * [G dv] at v_col0.  Query / key heads: RMS norm over d with the weights wq / wk [d] (shared by the heads; null = no norm), then rotation
+ * of the first rot_dims entries (pairs (i, i + rot_dims / 2)) by pos * freq[i] (freq: rot_dims / 2 doubles on the device) with cosine and
+ * sine multiplied by `mag`.  Value heads: divided by their root mean square over dv when norm_v.  Queries -> q_out [T, q_ld]; keys ->
+ * k_cache, values -> v_cache at the token's (block, slot) (see the file header for the plane addressing). */
+int dsb200_head_norm_rotary_append(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* wq,
+                                   const float* wk, const double* freq, float mag, const int* tok_seq, const int* tok_pos,
+                                   const int* block_table, int bt_stride, int block_size, void* k_cache,
+                                   long long k_block_stride, void* v_cache, long long v_block_stride, void* q_out,
+                                   long long q_ld, int n_tokens, int H, int G, int d, int dv, int rot_dims, float eps,
+                                   int norm_v, int dtype, dsb200_stream_t stream);
+/* out[t, h dv + c] = sum_j p_j v_j[c] over the keys j <= pos(t) of the token's sequence, p_j = exp(s_j) / (sink + sum_j exp(s_j)),
+ * s_j = scale q_h . k_j, soft-capped as cap tanh(s_j / cap) when cap > 0.  q [T, q_ld] (H heads of d); query head h reads key/value head
+ * h / (H / G); out [T, out_ld] (H heads of dv).  CUDA cores, fp32 scores and accumulation, any sizes; dtype 0 = bf16, 1 = fp32. */
+int dsb200_sink_attention(const void* q, long long q_ld, const void* k_cache, long long k_block_stride,
+                          const void* v_cache, long long v_block_stride, const int* tok_seq, const int* tok_pos,
+                          const int* block_table, int bt_stride, int block_size, void* out, long long out_ld, int n_tokens,
+                          int H, int G, int d, int dv, float scale, float cap, float sink, int dtype,
                           dsb200_stream_t stream);
 
 /* ---- csrc/random_ltd/token_ops.cu */
