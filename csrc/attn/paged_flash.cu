@@ -50,6 +50,10 @@ __device__ __forceinline__ float ex2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// cap tanh(score / cap) in the exp2 domain (see Params::cap_l2): two MUFU operations per score; 2^(..) = inf gives cap_l2, 0 gives -cap_l2
+__device__ __forceinline__ float soft_cap_l2(float raw, float cap_in, float cap_l2) {
+  return fmaf(-cap_l2, __fdividef(2.f, 1.f + ex2_fast(raw * cap_in)), cap_l2);
+}
 
 struct Params {
   const int* tok_seq;      // [T] sequence slot of every token of the ragged batch
@@ -68,6 +72,10 @@ struct Params {
   long long out_ld;    // elements between the output rows of consecutive tokens (hq * D when the output is dense)
   float out_scale;     // the normalised output is multiplied by this before it is rounded
   const float* alibi;  // optional [hq] ALiBi slopes: score += slope[head] * key position (BLOOM / MPT / falcon-rw); nullptr = none
+  // soft cap: score <- cap tanh(score / cap), formed in the exp2 domain as cap_l2 (1 - 2 / (1 + 2^(raw * cap_in))) with cap_l2 = cap log2(e)
+  // and cap_in = 2 log2(e) scale / cap (raw = q . k); cap_l2 = 0: no cap.  Not combined with ALiBi.
+  float cap_l2, cap_in;
+  float sink;          // added to the softmax denominator in units of exp(0): 1 = one more, valueless entry of score 0; 0 = plain softmax
   long long* trace;  // diagnostics only (DSB200_PF_TRACE=1): clock64 stamps of the first CTA with >= 8 pages, [page][8 events]
 };
 // events: 0 K landed (MMA thread)  1 P ready seen by the MMA thread  2 S ready seen by softmax  3 P published  4 partial O read
@@ -292,7 +300,8 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // the running maximum / exponent arithmetic below uses a scale of 1
       const bool has_alibi = p.alibi != nullptr;
       const float slope_l2 = (has_alibi && live) ? p.alibi[kvh * p.group + g] * 1.4426950408889634f : 0.f;
-      const float sl2 = has_alibi ? 1.f : p.scale_log2;
+      const bool has_cap = p.cap_l2 > 0.f;  // capped scores are formed in the exp2 domain too
+      const float sl2 = (has_alibi || has_cap) ? 1.f : p.scale_log2;
       __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(smem + SMEM::X_OFF);  // [part][row]
       const uint32_t bar_a = 1 + q4, bar_b = 5 + q4;  // the 4 warps (128 threads) that share the rows of this quarter
       const uint32_t o_addr = TM_O + part * DQ + lane_off;
@@ -331,6 +340,10 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t sv[32];  // the thread's scores stay in registers for both passes
         tmem_ld_32x32(s_addr, sv);
         tmem_ld_wait();
+        if (has_cap) {  // before the mask: a hidden key must stay at -inf, not at -cap
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[i] = __float_as_uint(soft_cap_l2(__uint_as_float(sv[i]), p.cap_in, p.cap_l2));
+        }
         const int hidden = first - key0;  // keys [0, hidden) of the thread's 32 precede the local window ...
         const int kept = p.keep - key0;   // ... but its keys [0, kept) are kept first keys and stay visible
         if (!__all_sync(0xffffffffu, visible >= 32 && hidden <= 0)) {  // only the diagonal page(s) / the window's first page(s)
@@ -417,6 +430,7 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (live) {
         const int t = t0 + ti, head = kvh * p.group + g;
         if (!partial) {
+          if (p.sink > 0.f) l_run += p.sink * exp2f(m_run == -INFINITY ? 0.f : -m_run);  // the sink's score is 0 (splits: added by the merge)
           const float inv_l = p.out_scale / l_run;
           __nv_bfloat16* dst = p.out + static_cast<size_t>(t) * p.out_ld + head * D + part * DQ;
 #pragma unroll
@@ -681,7 +695,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int limit[CPT], first[CPT];     // keys [first, limit) are visible to column c
       float slope_l2[CPT];            // ALiBi slope of the column's head, exp2 domain (0 without ALiBi)
       const bool has_alibi = p.alibi != nullptr;
-      const float sl2 = has_alibi ? 1.f : p.scale_log2;
+      const bool has_cap = p.cap_l2 > 0.f;
+      const float sl2 = (has_alibi || has_cap) ? 1.f : p.scale_log2;
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
         m_run[i] = -INFINITY;
@@ -705,7 +720,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // then the 4 lane-quarter warps meet in shared memory
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
-          s[i] = (key >= limit[i] || (key < first[i] && key >= p.keep)) ? -INFINITY : __uint_as_float(sv[i]);
+          const float raw = has_cap ? soft_cap_l2(__uint_as_float(sv[i]), p.cap_in, p.cap_l2) : __uint_as_float(sv[i]);
+          s[i] = (key >= limit[i] || (key < first[i] && key >= p.keep)) ? -INFINITY : raw;
           if (has_alibi) s[i] = fmaf(s[i], p.scale_log2, slope_l2[i] * static_cast<float>(key));
           const uint32_t bits = __float_as_uint(s[i]);
           const uint32_t r = __reduce_max_sync(0xffffffffu, bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
@@ -784,10 +800,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
         const int c = c0 + i;
-        const float l = (xl[c] + xl[NQ + c]) + (xl[2 * NQ + c] + xl[3 * NQ + c]);
+        float l = (xl[c] + xl[NQ + c]) + (xl[2 * NQ + c] + xl[3 * NQ + c]);
         if (c < nq) {
           const int t = t0 + c / p.group, head = kvh * p.group + c % p.group;
           if (!partial) {
+            if (p.sink > 0.f) l += p.sink * exp2f(m_run[i] == -INFINITY ? 0.f : -m_run[i]);  // the sink's score is 0 (splits: added by the merge)
             p.out[static_cast<size_t>(t) * p.out_ld + head * D + row] = __float2bfloat16_rn(__uint_as_float(ov[i]) / l * p.out_scale);
           } else {
             const size_t slot = (static_cast<size_t>(t) * p.hq + head) * p.n_splits + split;
@@ -820,7 +837,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // out[t][h][:] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s ; one warp per (token, head)
 template <int D>
 __global__ void combine_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                                      int rows, int n_splits, int hq, long long out_ld, float out_scale) {
+                                      int rows, int n_splits, int hq, long long out_ld, float out_scale, float sink) {
   const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (wid >= rows) return;
   constexpr int EPL = D / 32;
@@ -839,6 +856,7 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_o, const fl
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[e] = fmaf(w, part_o[slot * D + lane * EPL + e], acc[e]);
   }
+  if (sink > 0.f) L += sink * exp2f(M == -INFINITY ? 0.f : -M);  // a softmax with a sink: its score is 0
   const float inv = out_scale / L;
   __nv_bfloat16* dst = out + static_cast<size_t>(wid / hq) * out_ld + (wid % hq) * D;
 #pragma unroll
@@ -849,7 +867,8 @@ template <int D>
 static int launch(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                   int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms, int n_splits,
                   void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0, long long q_head_stride = 0,
-                  long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0, float out_scale = 1.f) {
+                  long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0, float out_scale = 1.f, float softcap = 0.f,
+                  float sink = 0.f) {
   using SMEM = Smem<D>;
   const int group = hq / hkv, nt_tile = BM / group;
   // the query tensor: [T][heads][D] rows of the fused projection by default; callers may give the number of heads that exist (a box
@@ -893,6 +912,8 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   p.T = T; p.hq = hq; p.hkv = hkv; p.group = group; p.nt_tile = nt_tile; p.block_size = block_size; p.max_blocks = max_blocks;
   p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.alibi = alibi; p.window = window;
   p.keep = window > 0 ? keep : 0; p.out_ld = out_ld ? out_ld : static_cast<long long>(hq) * D; p.out_scale = out_scale;
+  p.cap_l2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; p.cap_in = softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f;
+  p.sink = sink;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   p.trace = nullptr;
@@ -917,7 +938,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   if (n_splits > 1) {
     const int rows = T * hq;
     combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits, hq, p.out_ld,
-                                                                          p.out_scale);
+                                                                          p.out_scale, p.sink);
     DSB_CHECK_CUDA(cudaGetLastError());
   }
   return DSB_OK;
@@ -928,7 +949,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
                          int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms,
                          int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0,
                          long long q_head_stride = 0, long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0,
-                         float out_scale = 1.f) {
+                         float out_scale = 1.f, float softcap = 0.f, float sink = 0.f) {
   constexpr int D = 128;
   const int group = hq / hkv, nt_tile = NQ / group;
   const int heads = q_heads ? q_heads : hq + 2 * hkv;
@@ -965,6 +986,8 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   p.T = T; p.hq = hq; p.hkv = hkv; p.group = group; p.nt_tile = nt_tile; p.block_size = block_size; p.max_blocks = max_blocks;
   p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.trace = nullptr; p.alibi = alibi; p.window = window;
   p.keep = window > 0 ? keep : 0; p.out_ld = out_ld ? out_ld : static_cast<long long>(hq) * D; p.out_scale = out_scale;
+  p.cap_l2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; p.cap_in = softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f;
+  p.sink = sink;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   if (want_trace) {
@@ -988,7 +1011,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   if (n_splits > 1) {
     const int rows = T * hq;
     combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits, hq, p.out_ld,
-                                                                          p.out_scale);
+                                                                          p.out_scale, p.sink);
     DSB_CHECK_CUDA(cudaGetLastError());
   }
   return DSB_OK;
@@ -1100,4 +1123,32 @@ DSB_EXPORT int dsb200_paged_flash_window(const void* q, long long q_tok_stride, 
                               max_atoms, n_splits, scratch, nullptr, window, stream, hq, head_dim, q_tok_stride, 2, keep_first, out_ld, out_scale);
   return paged::launch<64>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
                            max_atoms, n_splits, scratch, nullptr, window, stream, hq, head_dim, q_tok_stride, 2, keep_first, out_ld, out_scale);
+}
+
+// Causal attention with soft-capped scores and a sink in the softmax, on the tensor-core kernels: weights exp(s_j) / (sink + sum_j exp(s_j)),
+// s_j = scale q . k_j, capped as softcap tanh(s_j / softcap) when softcap > 0 (two more MUFU operations per score).  q [n_tokens][hq][head_dim]
+// bf16 at q_tok_stride elements per token (a multiple of 8), kv_cache [num_blocks][2][block_size][hkv][head_dim] bf16; out rows at out_ld
+// elements per token (a multiple of 8).  decode != 0 selects the small-atom kernel (head_dim 128, q:kv head ratios dividing 16).
+DSB_EXPORT int dsb200_paged_flash_sink(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld, const int* tok_seq,
+                                       const int* tok_pos, const int* block_table, int n_tokens, int hq, int hkv, int head_dim, int block_size,
+                                       int max_blocks_per_seq, int num_blocks, float scale, float softcap, float sink, int max_atoms, int n_splits,
+                                       void* scratch, int decode, cudaStream_t stream) {
+  using namespace dsb;
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(head_dim == 64 || head_dim == 128, "paged_flash_sink: head_dim %d unsupported (64 or 128)", head_dim);
+  DSB_REQUIRE(hq % hkv == 0 && 128 % (hq / hkv) == 0, "paged_flash_sink: q/kv head ratio %d must divide 128", hq / hkv);
+  DSB_REQUIRE(block_size >= 8 && block_size <= 128 && 128 % block_size == 0, "paged_flash_sink: KV block size %d must divide 128", block_size);
+  DSB_REQUIRE(softcap >= 0.f && sink >= 0.f && q_tok_stride % 8 == 0 && out_ld % 8 == 0 && out_ld >= static_cast<long long>(hq) * head_dim,
+              "paged_flash_sink: cap %f, sink %f, strides %lld / %lld", softcap, sink, q_tok_stride, out_ld);
+  DSB_REQUIRE(max_atoms >= 1 && n_splits >= 1 && n_splits <= 64 && scratch != nullptr, "paged_flash_sink: bad max_atoms / n_splits / scratch");
+  if (decode) {
+    DSB_REQUIRE(head_dim == 128 && 16 % (hq / hkv) == 0, "paged_flash_sink: the decode kernel takes head_dim 128 and head ratios dividing 16");
+    return paged::launch_decode(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
+                                max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink);
+  }
+  if (head_dim == 128)
+    return paged::launch<128>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
+                              max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink);
+  return paged::launch<64>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
+                           max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink);
 }

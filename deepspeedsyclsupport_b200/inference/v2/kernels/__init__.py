@@ -499,6 +499,7 @@ native.register_sigs({
     "dsb200_tied_gate_scan": "p l iii pp p pp iiii i p",
     "dsb200_head_norm_rotary_append": "p l iii pp p f ppp ii p l p l p l iiiii i f i i p",
     "dsb200_sink_attention": "p l p l p l ppp ii p l iiiii fff i p",
+    "dsb200_paged_flash_sink": "p l pp l ppp iiiiiii fff ii p i p",
 }, restype_long=("dsb200_scan_state_floats", ))
 
 
@@ -683,4 +684,32 @@ def sink_attention(q, k_plane, v_plane, tok_seq, tok_pos, block_table, block_siz
                                                     native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0), int(block_size),
                                                     native.ptr(out), out.stride(0), T, H, G, d, dv, float(scale), float(softcap), float(sink),
                                                     _dt(q), native.stream_ptr()))
+    return out
+
+
+def paged_flash_sink_ok(q, cache, out, H, G, d, dv):
+    """Whether the tensor-core kernels take this attention: bf16, equal key / value head sizes of 64 / 128 in one two-plane cache tensor, a
+    q:kv head ratio dividing 128, cache blocks dividing 128, 16-byte aligned rows."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and d == dv and d in (64, 128) and
+            cache.dim() == 5 and H % G == 0 and 128 % (H // G) == 0 and cache.shape[2] >= 8 and 128 % cache.shape[2] == 0 and q.stride(0) % 8 == 0 and
+            out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and os.environ.get("DSB200_PAGED_FLASH", "1") != "0")
+
+
+def paged_flash_sink(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, scale, softcap=0.0, sink=1.0, decode=False, max_context=None, n_splits=None):
+    """`sink_attention` on the tensor cores (csrc/attn/paged_flash.cu: TMA pages through the block table, S / P / O in TMEM) for a two-plane
+    cache [blocks, 2, block_size, G, d].  `decode`: (almost) one token per sequence -- the small-atom kernel."""
+    T = q.shape[0]
+    bs, group = cache.shape[2], H // G
+    decode = bool(decode) and d == 128 and 16 % group == 0 and os.environ.get("DSB200_PAGED_DECODE", "1") != "0"
+    nt = (16 if decode else 128) // group
+    max_atoms = max(1, min(T, (T + nt - 1) // nt + block_table.shape[0]))
+    if n_splits is None:
+        pages = -(-(max_context if max_context is not None else block_table.shape[1] * bs) // 128)
+        n_splits = _pick_splits(T, H, d, max_atoms * G, pages, page_us=0.45 if decode else 0.7)
+    nbytes = native.lib().dsb200_paged_flash_scratch_bytes(T, H, d, max_atoms, n_splits)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    native.check(native.lib().dsb200_paged_flash_sink(native.ptr(q), q.stride(0), native.ptr(cache), native.ptr(out), out.stride(0), native.ptr(tok_seq),
+                                                      native.ptr(tok_pos), native.ptr(block_table), T, H, G, d, bs, block_table.shape[1], cache.shape[0],
+                                                      float(scale), float(softcap), float(sink), max_atoms, n_splits, native.ptr(scratch), int(decode),
+                                                      native.stream_ptr()), 2 + (n_splits > 1))
     return out

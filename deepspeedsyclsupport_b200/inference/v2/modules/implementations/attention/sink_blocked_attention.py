@@ -96,4 +96,7 @@ class DSSinkBlockedAttention(DSSelfAttentionBase):
         K.head_norm_rotary_append(proj, q0, k0, v0, norm_q if c.qk_norm else None, norm_k if c.qk_norm else None, self._freq if c.rotate_dim else None,
                                   self._mag, batch.tok_seq(), batch.tok_pos(), batch.block_table(), bs, kp, vp, q, H, G, d, dv, c.rotate_dim, c.eps,
                                   norm_v=c.v_norm)
+        if v_cache is None and K.paged_flash_sink_ok(q, k_cache, out, H, G, d, dv):
+            return K.paged_flash_sink(q, k_cache, batch.tok_seq(), batch.tok_pos(), batch.block_table(), out, H, G, d, c.scale, c.softcap, c.sink,
+                                      decode=batch.current_tokens <= 2 * batch.current_sequences)
         return K.sink_attention(q, kp, vp, batch.tok_seq(), batch.tok_pos(), batch.block_table(), bs, out, H, G, d, dv, c.scale, c.softcap, c.sink)

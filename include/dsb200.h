@@ -165,6 +165,15 @@ int dsb200_paged_flash_window(const void* q, long long q_tok_stride, const void*
                               int hkv, int head_dim, int block_size, int max_blocks_per_seq, int num_blocks, float scale,
                               float out_scale, int window, int keep_first, int max_atoms, int n_splits, void* scratch,
                               int decode, dsb200_stream_t stream);
+/* Causal attention with soft-capped scores and a sink in the softmax, on the tensor-core kernels: weights exp(s_j) / (sink + sum_j exp(s_j)),
+ * s_j = scale q . k_j, capped as softcap tanh(s_j / softcap) when softcap > 0 (two more MUFU operations per score).  q [n_tokens][hq][head_dim]
+ * bf16 at q_tok_stride elements per token (a multiple of 8), kv_cache [num_blocks][2][block_size][hkv][head_dim] bf16; out rows at out_ld
+ * elements per token (a multiple of 8).  decode != 0 selects the small-atom kernel (head_dim 128, q:kv head ratios dividing 16). */
+int dsb200_paged_flash_sink(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld,
+                            const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int hq, int hkv,
+                            int head_dim, int block_size, int max_blocks_per_seq, int num_blocks, float scale,
+                            float softcap, float sink, int max_atoms, int n_splits, void* scratch, int decode,
+                            dsb200_stream_t stream);
 
 /* ---- csrc/comm/symm.cu */
 /* ---- allocation / mapping (host pointers unless noted) */

@@ -285,6 +285,49 @@ def test_a_far_key_a_sink_and_the_causal_limit_show_in_the_output(far, d, dv, G)
         assert float(want[far - 1].abs().max()) < 0.05 * float(want[far].abs().max())  # the sink held the weight until the strong key came
 
 
+@gpu
+@pytest.mark.parametrize("d,G,group", [(64, 2, 2), (128, 1, 4), (128, 2, 1)])
+@pytest.mark.parametrize("cap,sink", [(12.0, 1.0), (0.0, 1.0), (30.0, 0.0)])
+@pytest.mark.parametrize("far", [5, 127, 128, 300])
+def test_tensor_core_kernels_agree_with_the_oracle(far, cap, sink, d, G, group):
+    """bf16, equal head sizes of 64 / 128 in a two-plane cache: the prefill and the small-atom decode kernel (with and without splits along
+    the keys) against the float64 formula, with ONE strong key among hundreds of opposed ones at a page's last / first row and far away --
+    found by the queries at and behind it, not by the one before it -- with and without cap and sink."""
+    K = _K()
+    H, T, block = G * group, 400, 16
+    g = torch.Generator().manual_seed(far + d)
+    q = torch.randn(T, H, d, generator=g, dtype=F64) * 0.3
+    k = torch.randn(T, G, d, generator=g, dtype=F64) * 0.3
+    v = torch.randn(T, G, d, generator=g, dtype=F64)
+    u = torch.randn(d, generator=g, dtype=F64)
+    u = u / u.norm()
+    q[:] = q - (q @ u)[..., None] * u + 2.0 * u
+    k[:] = k - (k @ u)[..., None] * u - 2.0 * u
+    k[far] += 6.0 * u
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    scale = 1.3
+    want = O.sink_attention(q.double(), k.double(), v.double(), scale, cap, sink)
+    perm = torch.randperm(40, generator=g)[:T // block + 1].tolist()
+    cache = torch.zeros(40, 2, block, G, d, dtype=torch.bfloat16, device="cuda")
+    for j in range(T):
+        cache[perm[j // block], 0, j % block] = k[j].cuda()
+        cache[perm[j // block], 1, j % block] = v[j].cuda()
+    cases = [(list(range(T - 150, T)), False, None), (list(range(max(far - 40, 0), min(far + 60, T))), False, 3)]
+    cases += [([p], dec, sp) for p in (far - 1, far, far + 1, T - 1) if 0 <= p < T for dec in (False, True) for sp in (None, 2)]
+    for rows, decode, splits in cases:
+        b = _Batch([(0, rows[0], len(rows), perm)], block, max_blocks=40)
+        wide = torch.zeros(len(rows), H * d + 8, dtype=torch.bfloat16, device="cuda")
+        qq = q[rows].reshape(len(rows), H * d).cuda()
+        assert K.paged_flash_sink_ok(qq, cache, wide[:, :H * d], H, G, d, d)
+        K.paged_flash_sink(qq, cache, b.tok_seq(), b.tok_pos(), b.block_table(), wide[:, :H * d], H, G, d, scale, cap, sink, decode=decode, n_splits=splits)
+        got = wide[:, :H * d].cpu().double().view(len(rows), H, d)
+        assert float(wide[:, H * d:].abs().max()) == 0
+        err = (got - want[rows]).abs().max() / want[rows].abs().max()
+        assert float(err) < 2e-2, (rows[0], decode, splits, float(err))
+    if sink > 0 and far >= 1:
+        assert float(want[far - 1].abs().max()) < 0.2 * float(want[far].abs().max())  # the sink held the weight until the strong key came
+
+
 def _gate_module(m, dt):
     from deepspeedsyclsupport_b200.inference.v2.inference_utils import DtypeEnum
     from deepspeedsyclsupport_b200.inference.v2.modules import heuristics
