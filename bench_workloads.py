@@ -745,4 +745,229 @@ def run_kulanex(args):
           flush=True)
 
 
-WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun, "kulanex": run_kulanex}
+# ---- Pudinex beside a Kulanex and a Mixtral of equal size
+PUDINEX_SIZES = {  # width, layers, attention heads, head_dim, kv heads, experts, top, ff, vocab
+    "s": (2048, 4, 16, 128, 4, 8, 2, 1024, 32000),
+    "m": (4096, 4, 32, 128, 8, 8, 2, 2048, 32000),
+}
+PUDINEX_IDENTITY = 2
+
+
+def _pudinex_state(torch, dev, W, L, H, d, hkv, E, top, ff, V):
+    """Layers alternate 'hgrn2' (H heads, d x d states) and 'attention' (H:hkv heads of d, half of every head rotated, soft cap 50), all with
+    the MoE feed-forward (E experts + 2 identity experts, a shared expert of the experts' size); two norm parts."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "identity": PUDINEX_IDENTITY, "top": top}, "shared": {"ff": ff}}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": H, "kv_heads": hkv, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 50.0,
+                     "rot": {"base": 1e6, "dims": d // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    rec = {"type": "hgrn2", "mlp": moe, "mixer": {"heads": H, "dim": d, "vdim": d}}
+    cfg = {"architecture": "Pudinex", "vocab": V, "width": W, "norm": {"eps": 1e-6, "groups": 2}, "embedding": {"scale": 1.0},
+           "layers": [rec if i % 2 == 0 else att for i in range(L)]}
+
+    def r(*shape, std=0.02, mean=0.0):
+        return torch.empty(*shape, device=dev, dtype=torch.bfloat16).normal_(mean, std)
+
+    sd = {"embed": r(V, W, std=1.0), "final.norm": r(W, mean=1.0), "head": r(V, W)}
+    for i in range(L):
+        p = f"l{i}."
+        sd.update({p + "norm1": r(W, mean=1.0), p + "mlp.router": r(E + PUDINEX_IDENTITY, W, std=0.5), p + "mlp.correction": r(E + PUDINEX_IDENTITY),
+                   p + "mlp.shared.gate": r(ff, W), p + "mlp.shared.up": r(ff, W), p + "mlp.shared.down": r(W, ff)})
+        for e in range(E):
+            sd.update({p + f"mlp.e{e}.gate": r(ff, W), p + f"mlp.e{e}.up": r(ff, W), p + f"mlp.e{e}.down": r(W, ff)})
+        a = p + "mix."
+        if i % 2 == 0:
+            sd.update({a + "q": r(H * d, W), a + "f": r(H * d, W), a + "f.b": r(H * d, mean=2.0, std=1.0), a + "lower": r(H * d, mean=0.5, std=0.1), a + "v": r(H * d, W),
+                       a + "norm": r(d, mean=1.0), a + "o": r(W, H * d)})
+        else:
+            sd.update({a + "q": r(H * d, W), a + "k": r(hkv * d, W), a + "v": r(hkv * d, W), a + "q.norm": r(d, mean=1.0), a + "k.norm": r(d, mean=1.0), a + "o": r(W, H * d)})
+    return cfg, sd
+
+
+def _pudinex_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, T, ctx, n_dec):
+    """Every kernel of the design beside the like kernel of the closest family (Kulanex; the plain Mixtral path where Kulanex has none),
+    isolated, with the fraction of the measured roofline (HBM copy bandwidth for the streaming kernels, cuBLAS bf16 rate for attention
+    prefill)."""
+    from deepspeedsyclsupport_b200.inference.v2 import kernels as K
+    from deepspeedsyclsupport_b200.ops import fused_ops as FO
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, ms, like, like_ms, nbytes=None, like_bytes=None, flops=None, like_flops=None):
+        def frac(ms_, b, f):
+            return round(max((b or 0) / hbm, (f or 0) / tf) / (ms_ * 1e-3), 3)
+        rows.append({"kernel": name, "ms": round(ms, 4), "roofline_frac": frac(ms, nbytes, flops), "like": like, "like_ms": round(like_ms, 4),
+                     "like_roofline_frac": frac(like_ms, like_bytes if like_bytes is not None else nbytes, like_flops if like_flops is not None else flops)})
+
+    x32, y, y32, g32 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev), torch.randn(W, device=dev)
+    add("stream_group_norm (2 parts; bf16 + fp32 branch in, bf16 + fp32 copy out)",
+        _event_ms(torch, lambda: K.stream_group_norm(x32, (y, ), y32, g32, 2, 1e-6, fp32_copy=True), 20, flush),
+        "sandwich_norm post-norm into the fp32 stream + bf16 copy (Kulanex)",
+        _event_ms(torch, lambda: K.sandwich_norm(x32, y, g32, 1.0, None, 0.0, 1e-6, y_mult=0.5, plain_out=True), 20, flush),
+        nbytes=T * W * (4 + 4 + 2 + 4 + 2 + 4), like_bytes=T * W * (4 + 4 + 2 + 2))
+    n_out = E + PUDINEX_IDENTITY
+    lg, corr = torch.randn(T, n_out, device=dev), torch.randn(n_out, device=dev) * 0.01
+    add("grouped_topk_gating (softmax, correction, renormalised)", _event_ms(torch, lambda: K.grouped_topk_gating(lg, top, corr, normalize=True), 20, flush),
+        "grouped_topk_gating (sigmoid scores; Kulanex)", _event_ms(torch, lambda: K.grouped_topk_gating(lg, top, sigmoid_scores=True), 20, flush),
+        nbytes=T * (n_out * 4 + top * 12))
+    counts, scores, asg, off = K.grouped_topk_gating(lg, top, corr, normalize=True)
+    h = torch.randn(T, W, device=dev).to(bf)
+    moe_in, cumsum, slots = K.moe_scatter_rows(h, counts, asg, off)
+    dn = torch.randn(T * top, W, device=dev).to(bf)
+    add("moe_gather_rows (identity experts read the fp32 input)", _event_ms(torch, lambda: K.moe_gather_rows(dn, scores, slots, asg, E, y32), 20, flush),
+        "moe_gather_rows (plain sum; Kulanex)", _event_ms(torch, lambda: K.moe_gather_rows(dn, None, slots), 20, flush), nbytes=T * W * (2 * top + 4))
+    gu = torch.randn(T, 3 * H * d + 2 * ff, device=dev).to(bf)
+    wide = torch.empty(T, H * d + ff, device=dev, dtype=bf)
+    gpair = torch.randn(T, 2 * ff, device=dev).to(bf)
+    add("clamped_swish_gate_cols (column ranges of the fused projection)", _event_ms(torch, lambda: K.clamped_swish_gate_cols(gu, 3 * H * d, 3 * H * d + ff, ff, wide[:, H * d:], 1.0, float("inf"), 0.0), 20, flush),
+        "gated_act (silu; Mixtral)", _event_ms(torch, lambda: FO.gated_act(gpair, "silu"), 20, flush), nbytes=T * ff * 6)
+    bs = 128
+    from deepspeedsyclsupport_b200.inference.v2.modules.configs import RampRotaryScalingConfig
+    from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.sink_blocked_attention import ramp_scaled_frequencies
+    from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.windowed_conv_attention import scaled_rotary_frequencies
+    freq, mag = ramp_scaled_frequencies(d // 2, 1e6, RampRotaryScalingConfig(factor=8.0, original=8192, fast=32.0, slow=1.0))
+    freq = freq.to(dev)
+    wfreq = scaled_rotary_frequencies(d // 2, 1e6, None).to(dev)
+    inv_freq = (1e6 ** (-torch.arange(0, d, 2, device=dev, dtype=torch.float32) / d))
+    for label, n_seq, new, seen in (("prefill", max(1, T // 2048), min(T, 2048), ctx), ("decode", n_dec, 1, ctx)):
+        per = -(-(seen + new) // bs)
+        nb = n_seq * per
+        bt = torch.arange(nb, dtype=torch.int32, device=dev).view(n_seq, per)
+        tok_seq = torch.arange(n_seq, dtype=torch.int32, device=dev).repeat_interleave(new)
+        tok_pos = (seen + torch.arange(new, dtype=torch.int32, device=dev)).repeat(n_seq)
+        desc = torch.tensor([[i * new, new, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        Tn = n_seq * new
+        dec = label == "decode"
+        kv = torch.randn(nb, 2, bs, hkv, d, device=dev).to(bf)
+        qkv = torch.randn(Tn, (H + 2 * hkv) * d, device=dev).to(bf)
+        nw = torch.randn(d, device=dev)
+        qo = torch.empty(Tn, H * d, device=dev, dtype=bf)
+        planes = K.cache_planes(kv)
+        # per-head norms + rotation + append vs the convolving prepare of Kulanex and the plain rotary append
+        C = (H + hkv) * d
+        cw, cn = torch.randn(C, 4, device=dev), torch.randn(C, device=dev)
+        cstate = torch.zeros(n_seq, 3, C, device=dev, dtype=bf)
+
+        def kprep():
+            K.window_qk_prepare(qkv, 0, H * d, cw, cw[H * d:], cn, cn[H * d:], cstate, desc, tok_seq, tok_pos, bt, kv, qo, wfreq, H, hkv, d, 4, d // 2, 1e-6)
+            K.conv_state_update(qkv, 0, C, cstate, 0, desc, n_seq, 4)
+        ms_prep = _event_ms(torch, lambda: K.head_norm_rotary_append(qkv, 0, H * d, (H + hkv) * d, nw, nw, freq, mag, tok_seq, tok_pos, bt, bs, planes[0], planes[1], qo,
+                                                                     H, hkv, d, d, d // 2, 1e-6), 10, flush)
+        add(f"head_norm_rotary_append, {label}", ms_prep, f"window_qk_prepare + conv_state_update (Kulanex), {label}", _event_ms(torch, kprep, 10, flush),
+            nbytes=Tn * (H + 2 * hkv) * d * 4, like_bytes=Tn * (C * 2 + H * d * 2 + 2 * hkv * d * 2))
+        add(f"head_norm_rotary_append, {label} ", ms_prep, f"kv_rotary_append (Mixtral), {label}",
+            _event_ms(torch, lambda: K.kv_rotary_append(qkv, kv, tok_seq, tok_pos, bt, inv_freq, H, hkv, d), 10, flush), nbytes=Tn * (H + 2 * hkv) * d * 4)
+        keys = n_seq * new * (seen + (new + 1) / 2)
+        out = torch.empty(Tn, H * d, device=dev, dtype=bf)
+        abytes = n_seq * (seen + new) * hkv * d * 4 + Tn * H * d * 4
+        add(f"attention, soft cap 50 + sink, tcgen05, {label} (GQA {H}:{hkv})",
+            _event_ms(torch, lambda: K.paged_flash_sink(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, d ** -0.5, 50.0, 1.0, decode=dec), 10, flush),
+            f"paged flash attention, causal, {label} (Mixtral)",
+            _event_ms(torch, lambda: K.paged_attention(qkv, kv, tok_seq, tok_pos, bt, H, hkv, d, d ** -0.5, decode=dec), 10, flush), nbytes=abytes, flops=4.0 * keys * H * d)
+        add(f"attention, sink only (no cap), tcgen05, {label}",
+            _event_ms(torch, lambda: K.paged_flash_sink(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, d ** -0.5, 0.0, 1.0, decode=dec), 10, flush),
+            f"paged flash attention, causal, {label} (Mixtral)", rows[-1]["like_ms"], nbytes=abytes, flops=4.0 * keys * H * d)
+        # recurrent scan beside Kulanex's delta rule on a state of the same size
+        proj = torch.randn(Tn, 3 * H * d, device=dev).to(bf)
+        fb, lo = torch.full((H * d, ), 2.0, device=dev), torch.full((H * d, ), 0.5, device=dev)
+        sS = torch.zeros(n_seq, H, K.scan_state_floats(d, d), device=dev)
+        qn, kn, vv = torch.randn(Tn, H * d, device=dev) * 0.1, torch.randn(Tn, H * d, device=dev) * 0.1, torch.randn(Tn, H * d, device=dev)
+        bp, ap = torch.sigmoid(torch.randn(Tn, H, device=dev)), torch.exp(-0.08 * torch.nn.functional.softplus(torch.randn(Tn, H * d, device=dev) - 2.0))
+        dS = torch.zeros(n_seq, H, K.scan_state_floats(d, d), device=dev)
+        state_b = n_seq * H * d * d * 8
+        add(f"tied_gate_scan ({H} x {d} x {d}), {label}", _event_ms(torch, lambda: K.tied_gate_scan(proj, 0, H * d, 2 * H * d, fb, lo, desc, n_seq, sS, H, d, d), 5, flush),
+            f"delta_rule_scan ({H} x {d} x {d}; Kulanex), {label}", _event_ms(torch, lambda: K.delta_rule_scan(qn, kn, vv, bp, ap, desc, n_seq, dS, H, H, d, d), 5, flush),
+            nbytes=Tn * H * d * (3 * 2 + 4) + state_b, like_bytes=Tn * H * (4 * d * 4 + 4) + Tn * H * d * 4 + state_b)
+        o32, gt, og = torch.randn(Tn, H * d, device=dev), torch.randn(Tn, H * d, device=dev).to(bf), torch.empty(Tn, H * d, device=dev, dtype=bf)
+        add(f"head_norm_gate without a gate, {label}", _event_ms(torch, lambda: K.head_norm_gate(o32, nw, None, og, H, d, 1e-6, shared_weight=True), 10, flush),
+            f"head_norm_gate (Kulanex), {label}", _event_ms(torch, lambda: K.head_norm_gate(o32, nw, gt, og, H, d, 1e-6, shared_weight=True), 10, flush),
+            nbytes=Tn * H * d * 6, like_bytes=Tn * H * d * 8)
+    return rows
+
+
+def run_pudinex(args):
+    """Prefill and decode throughput of Pudinex through the FastGen engine at a few layer sizes, beside a Kulanex (the closest family: state
+    slots beside the paged cache) and a Mixtral of equal size (same width, layers, heads, experts, ff, top-k, vocabulary), plus the isolated
+    kernels of the design beside their likes."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import deepspeedsyclsupport_b200 as deepspeed
+    from deepspeedsyclsupport_b200 import comm as dist
+    from deepspeedsyclsupport_b200.inference.v2 import RaggedInferenceEngineConfig, build_engine_from_state_dict
+    from deepspeedsyclsupport_b200.ops import native
+    deepspeed.init_distributed()
+    assert dist.get_world_size() == 1, "--workload pudinex is a one-GPU comparison"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        peaks = dict(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), source="measured")
+    n_seqs, prompt, budget = min(args.sequences, 64), 1024, 4096
+    results, clocks, l0 = {}, None, native.launch_count
+    g = torch.Generator().manual_seed(11)
+    for name in (args.model.split(",") if args.model != "7b" else ["s", "m"]):
+        W, L, H, d, hkv, E, top, ff, V = PUDINEX_SIZES[name]
+        max_ctx = -(-(prompt + 4 * (args.steps + args.warmup) * 4 + 64) // 128) * 128
+        ecfg = RaggedInferenceEngineConfig(state_manager={"max_ragged_batch_size": budget, "max_ragged_sequence_count": n_seqs, "max_tracked_sequences": n_seqs,
+                                                          "max_context": max_ctx, "memory_config": {"mode": "allocate", "size": n_seqs * (max_ctx // 128) + 4}})
+        res = {}
+        for fam in ("pudinex", "kulanex", "mixtral"):
+            if fam == "pudinex":
+                cfg, sd = _pudinex_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            elif fam == "kulanex":
+                cfg, sd = _kulanex_state(torch, dev, W, L, H, d, hkv, 1024, E, top, ff, V)
+            else:
+                cfg, sd = _mixtral_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            eng = build_engine_from_state_dict(fam, cfg, sd, ecfg, dtype=torch.bfloat16)
+            n_params = sum(v.numel() for v in sd.values())
+            del sd
+            prompts = [torch.randint(0, V, (prompt, ), generator=g).pin_memory() for _ in range(n_seqs)]
+            uids = list(range(n_seqs))
+            state = {"live": False, "next": None}
+
+            def prefill():
+                if state["live"]:
+                    for u in uids:
+                        eng.flush(u)
+                per = budget // prompt
+                nxt = torch.zeros(n_seqs, dtype=torch.long)
+                for i in range(0, n_seqs, per):
+                    us = uids[i:i + per]
+                    nxt[i:i + len(us)] = eng.put(us, [prompts[u] for u in us]).argmax(-1).cpu()
+                state["live"], state["next"] = True, nxt
+
+            def decode():
+                nxt = state["next"]
+                for _ in range(4):
+                    nxt = eng.put(uids, [nxt[u:u + 1] for u in uids]).argmax(-1).cpu()
+                state["next"] = nxt
+
+            ms_p, _ = _timed(torch, dist, prefill, args.steps, 3)
+            ms_d, clk = _timed(torch, dist, decode, args.steps, args.warmup)
+            if fam == "pudinex":
+                clocks = clk
+            res[fam] = {"params_b": round(n_params / 1e9, 3), "prefill_tokens_per_s": round(n_seqs * prompt / ms_p * 1e3, 1), "prefill_ms": round(ms_p, 2),
+                        "decode_tokens_per_s": round(n_seqs * 4 / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d / 4, 3)}
+            del eng
+            torch.cuda.empty_cache()
+        for other in ("kulanex", "mixtral"):
+            res["pudinex_over_" + other] = {"prefill": round(res["pudinex"]["prefill_tokens_per_s"] / res[other]["prefill_tokens_per_s"], 3),
+                                            "decode": round(res["pudinex"]["decode_tokens_per_s"] / res[other]["decode_tokens_per_s"], 3)}
+        res["shape"] = {"width": W, "layers": L, "heads": H, "head_dim": d, "kv_heads": hkv, "experts": E, "identity": PUDINEX_IDENTITY, "top": top, "ff": ff}
+        res["kernels"] = _pudinex_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, 4096, 2048, n_seqs)
+        results[name] = res
+    launches = native.launch_count - l0
+    last = results[list(results)[-1]]
+    extra = {"results": results, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops", "source")},
+             "e2e": {"value": last["pudinex"]["decode_tokens_per_s"], "unit": "generated tokens/s", "h2d_bytes_per_step": n_seqs * 8, "d2h_bytes_per_step": n_seqs * 8},
+             "reference_arm": "none: the reference has no model of this design"}
+    config = {"model": "pudinex (random weights) beside kulanex and mixtral of equal size", "sizes": list(results), "sequences": n_seqs, "prompt_len": prompt,
+              "token_budget_per_forward": budget, "decode_steps_per_timed_step": 4, "kv_block": 128,
+              "l2_policy": "engine steps: weights exceed the 126 MB L2, no flush; isolated kernels: 256 MB write before every timed run"}
+    print(json.dumps(_line("generated tokens/sec Pudinex FastGen ragged decode, 1 GPU (prefill, a Kulanex and a Mixtral of equal size alongside)",
+                           last["pudinex"]["decode_tokens_per_s"], "tokens/s", 1, args, last["pudinex"]["decode_ms_per_step"], config, clocks, launches, extra)),
+          flush=True)
+
+
+WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun, "kulanex": run_kulanex, "pudinex": run_pudinex}

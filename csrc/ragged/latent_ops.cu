@@ -581,6 +581,28 @@ __global__ void clamped_swish_gate_cols_kernel(const T* __restrict__ gu, long lo
   }
 }
 
+// ... with F, both column offsets and both row strides multiples of 4 and 16-byte (fp32) / 8-byte (bf16) aligned bases: four outputs per thread
+template <typename T>
+__global__ void clamped_swish_gate_cols_vec_kernel(const T* __restrict__ gu, long long ld, int gate_col0, int up_col0, T* __restrict__ out,
+                                                   long long out_ld, long long rows, int F, float alpha, float limit, float shift) {
+  const int fv = F >> 2;
+  const long long n = rows * fv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i % fv) * 4;
+    const float4 g4 = load4(gu + r * ld + gate_col0 + c), u4 = load4(gu + r * ld + up_col0 + c);
+    const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
+    float o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float g = fminf(gs[k], limit);
+      const float u = fminf(fmaxf(us[k], -limit), limit);
+      o[k] = g * (1.f / (1.f + expf(-alpha * g))) * (u + shift);
+    }
+    store4(out + r * out_ld + c, make_float4(o[0], o[1], o[2], o[3]));
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, long long ld, int cols, long long n, float cap) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float* p = x + (i / cols) * ld + (i % cols);
@@ -1020,7 +1042,16 @@ DSB_EXPORT int dsb200_clamped_swish_gate_cols(const void* gu, long long ld, int 
                                               int F, float alpha, float limit, float shift, int dtype, cudaStream_t stream) {
   const long long n = rows * F;
   if (n == 0) return DSB_OK;
-  if (dtype == 0)
+  const int esz = dtype == 0 ? 2 : 4;
+  const bool vec = F % 4 == 0 && gate_col0 % 4 == 0 && up_col0 % 4 == 0 && ld % 4 == 0 && out_ld % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & (4 * esz - 1)) == 0;
+  if (vec && dtype == 0)
+    clamped_swish_gate_cols_vec_kernel<bf16><<<grid_for(n / 4, 256), 256, 0, stream>>>((const bf16*)gu, ld, gate_col0, up_col0, (bf16*)out, out_ld, rows, F,
+                                                                                     alpha, limit, shift);
+  else if (vec)
+    clamped_swish_gate_cols_vec_kernel<float><<<grid_for(n / 4, 256), 256, 0, stream>>>((const float*)gu, ld, gate_col0, up_col0, (float*)out, out_ld, rows, F,
+                                                                                      alpha, limit, shift);
+  else if (dtype == 0)
     clamped_swish_gate_cols_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gu, ld, gate_col0, up_col0, (bf16*)out, out_ld, rows, F, alpha,
                                                                               limit, shift);
   else

@@ -648,8 +648,17 @@ tied_gate_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int 
   auto split_v = [&](int x, int& tok, int& c) {
     if (lg_c >= 0) { tok = x >> lg_c; c = x & (ncol - 1); } else { tok = x / ncol; c = x - tok * ncol; }
   };
-  float pq[SCAN_PF], pf[SCAN_PF], pv[SCAN_PF];
-  const float *fb = f_bias + h * d, *lo = lower + h * d;
+  // fetch() only issues the loads of the next chunk (raw values, no use: the walk below runs while they are in flight); stage() turns them
+  // into q and f after the walk.  A thread's element e is the same channel in every chunk, so its bias and lower bound are loaded once.
+  T rq[SCAN_PF], rf[SCAN_PF], rv[SCAN_PF];
+  float e_bias[SCAN_PF], e_low[SCAN_PF];
+#pragma unroll
+  for (int e = 0; e < SCAN_PF; ++e) {
+    int tok, c;
+    split_qk(tid + e * nthr, tok, c);
+    e_bias[e] = tok < ch ? f_bias[h * d + c] : 0.f;
+    e_low[e] = tok < ch ? lower[h * d + c] : 0.f;
+  }
   auto fetch = [&](int t0) {
     const int cn = min(ch, sd.y - t0);
     const T* row0 = proj + static_cast<size_t>(sd.x + t0) * ld;
@@ -659,12 +668,11 @@ tied_gate_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int 
       split_qk(tid + e * nthr, tok, c);
       if (tok < cn) {
         const T* pr = row0 + static_cast<size_t>(tok) * ld;
-        pq[e] = siluf_(to_f(pr[q_col0 + h * d + c]));
-        const float l = lo[c];
-        pf[e] = l + (1.f - l) * sigmoidf_(to_f(pr[f_col0 + h * d + c]) + fb[c]);
+        rq[e] = pr[q_col0 + h * d + c];
+        rf[e] = pr[f_col0 + h * d + c];
       }
       split_v(tid + e * nthr, tok, c);
-      if (tok < cn) pv[e] = to_f(row0[static_cast<size_t>(tok) * ld + v_col0 + h * dv + col0 + c]);
+      if (tok < cn) rv[e] = row0[static_cast<size_t>(tok) * ld + v_col0 + h * dv + col0 + c];
     }
   };
   auto stage = [&](int t0, float* bq) {
@@ -677,11 +685,14 @@ tied_gate_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int 
       split_qk(tid + e * nthr, tok, c);
       if (tok < cn) {
         const int pos = tok * DP + staged_pos<RPT, R>(c);
-        bq[pos] = pq[e];
-        bf[pos] = pf[e];
+        // the query's silu is a projection's activation (fast exponential and division); the gate enters the recurrence: a full-precision
+        // exponential and a correctly rounded reciprocal (a true division would cost as much as the walk itself here)
+        const float zq = to_f(rq[e]);
+        bq[pos] = __fdividef(zq, 1.f + __expf(-zq));
+        bf[pos] = e_low[e] + (1.f - e_low[e]) * __frcp_rn(1.f + expf(-(to_f(rf[e]) + e_bias[e])));
       }
       split_v(tid + e * nthr, tok, c);
-      if (tok < cn) bv[tok * CBT + c] = pv[e];
+      if (tok < cn) bv[tok * CBT + c] = to_f(rv[e]);
     }
   };
   __syncthreads();  // the zeros are in place

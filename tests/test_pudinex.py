@@ -461,18 +461,20 @@ def test_router_with_identity_experts(experts, identity, top, ff, D, dt):
 @gpu
 @pytest.mark.parametrize("dt", DTYPES)
 def test_clamped_gate_on_column_ranges(dt):
-    """Gate and up as column ranges of a wider projection, the result into a column range of a wider buffer; limits that cut both."""
+    """Gate and up as column ranges of a wider projection, the result into a column range of a wider buffer; limits that cut both; odd offsets
+    (one value per thread) and offsets / sizes that are multiples of four (four values per thread)."""
     K = _K()
     g = torch.Generator().manual_seed(4)
-    proj = (torch.randn(13, 7 + 2 * 18 + 3, generator=g) * 2).to(dt).cuda()
-    wide = torch.zeros(13, 5 + 18, dtype=dt, device="cuda")
-    for alpha, limit, shift in ((1.702, 0.8, 1.0), (1.0, float("inf"), 0.0)):
-        K.clamped_swish_gate_cols(proj, 7, 7 + 18, 18, wide[:, 5:], alpha, limit, shift)
-        gt, up = proj[:, 7:25].cpu().double(), proj[:, 25:43].cpu().double()
-        gt, up = gt.clamp(max=limit), up.clamp(-limit, limit)
-        want = gt * torch.sigmoid(alpha * gt) * (up + shift)
-        assert torch.allclose(wide[:, 5:].cpu().double(), want, rtol=1e-5 if dt == torch.float32 else 1e-2, atol=1e-5 if dt == torch.float32 else 1e-2)
-        assert float(wide[:, :5].abs().max()) == 0
+    for c0, F, pad, lead in ((7, 18, 3, 5), (8, 20, 4, 4)):
+        proj = (torch.randn(13, c0 + 2 * F + pad, generator=g) * 2).to(dt).cuda()
+        wide = torch.zeros(13, lead + F, dtype=dt, device="cuda")
+        for alpha, limit, shift in ((1.702, 0.8, 1.0), (1.0, float("inf"), 0.0)):
+            K.clamped_swish_gate_cols(proj, c0, c0 + F, F, wide[:, lead:], alpha, limit, shift)
+            gt, up = proj[:, c0:c0 + F].cpu().double(), proj[:, c0 + F:c0 + 2 * F].cpu().double()
+            gt, up = gt.clamp(max=limit), up.clamp(-limit, limit)
+            want = gt * torch.sigmoid(alpha * gt) * (up + shift)
+            assert torch.allclose(wide[:, lead:].cpu().double(), want, rtol=1e-5 if dt == torch.float32 else 1e-2, atol=1e-5 if dt == torch.float32 else 1e-2)
+            assert float(wide[:, :lead].abs().max()) == 0
 
 
 # ------------------------------------------------------------------------------------------------------------ GPU: whole models
