@@ -869,6 +869,14 @@ def _pudinex_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, T, ctx, n_dec)
         add(f"attention, sink only (no cap), tcgen05, {label}",
             _event_ms(torch, lambda: K.paged_flash_sink(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, d ** -0.5, 0.0, 1.0, decode=dec), 10, flush),
             f"paged flash attention, causal, {label} (Mixtral)", rows[-1]["like_ms"], nbytes=abytes, flops=4.0 * keys * H * d)
+        # the CUDA-core kernel that serves fp32 runs and unequal key / value head sizes (here values half as wide as keys)
+        kc, vc = torch.randn(nb, bs, hkv, d, device=dev).to(bf), torch.randn(nb, bs, hkv, d // 2, device=dev).to(bf)
+        kp, vp = K.cache_planes(kc, vc)
+        oh = torch.empty(Tn, H * d // 2, device=dev, dtype=bf)
+        add(f"attention, soft cap 50 + sink, CUDA cores, values {d // 2} wide, {label}",
+            _event_ms(torch, lambda: K.sink_attention(qo, kp, vp, tok_seq, tok_pos, bt, bs, oh, H, hkv, d, d // 2, d ** -0.5, 50.0, 1.0), 3, flush),
+            f"paged flash attention, causal, {label} (Mixtral)", rows[-1]["like_ms"], nbytes=n_seq * (seen + new) * hkv * d * 3 + Tn * H * d * 3,
+            like_bytes=abytes, flops=3.0 * keys * H * d, like_flops=4.0 * keys * H * d)
         # recurrent scan beside Kulanex's delta rule on a state of the same size
         proj = torch.randn(Tn, 3 * H * d, device=dev).to(bf)
         fb, lo = torch.full((H * d, ), 2.0, device=dev), torch.full((H * d, ), 0.5, device=dev)
