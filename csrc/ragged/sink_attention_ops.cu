@@ -80,7 +80,8 @@ __global__ void head_norm_rotary_append_kernel(const T* __restrict__ proj, long 
                                                float mag, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                                const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ k_cache,
                                                long long k_block_stride, T* __restrict__ v_cache, long long v_block_stride, T* __restrict__ q_out,
-                                               long long q_ld, int n_tokens, int H, int G, int d, int dv, int rot, float eps, int norm_v) {
+                                               long long q_ld, int n_tokens, int H, int G, int d, int dv, int rot, float eps, int norm_v, int q_row,
+                                               int k_row, int v_row) {
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int per_tok = H + 2 * G;
   if (gw >= n_tokens * per_tok) return;
@@ -93,7 +94,7 @@ __global__ void head_norm_rotary_append_kernel(const T* __restrict__ proj, long 
   if (slot >= H + G) {  // a value head: its own root mean square, no weight
     const int g = slot - H - G;
     const T* src = row + v_col0 + g * dv;
-    T* dst = v_cache + cache_row * v_block_stride + (static_cast<long long>(in_block) * G + g) * dv;
+    T* dst = v_cache + cache_row * v_block_stride + (static_cast<long long>(in_block) * G + g) * v_row;
     float inv = 1.f;
     if (norm_v) {
       float s = 0.f;
@@ -102,14 +103,15 @@ __global__ void head_norm_rotary_append_kernel(const T* __restrict__ proj, long 
       inv = 1.f / sqrtf(s / static_cast<float>(dv) + eps);
     }
     for (int c = lane; c < dv; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv);
+    for (int c = dv + lane; c < v_row; c += 32) dst[c] = from_f<T>(0.f);  // rows padded to a width the tensor-core kernels take
     return;
   }
   const bool is_q = slot < H;
   const int head = is_q ? slot : slot - H;
   const T* src = row + (is_q ? q_col0 : k_col0) + head * d;
   const float* w = is_q ? wq : wk;
-  T* dst = is_q ? q_out + static_cast<long long>(t) * q_ld + head * d
-                : k_cache + cache_row * k_block_stride + (static_cast<long long>(in_block) * G + head) * d;
+  T* dst = is_q ? q_out + static_cast<long long>(t) * q_ld + head * q_row
+                : k_cache + cache_row * k_block_stride + (static_cast<long long>(in_block) * G + head) * k_row;
   float inv = 1.f;
   if (w != nullptr) {
     float s = 0.f;
@@ -130,6 +132,7 @@ __global__ void head_norm_rotary_append_kernel(const T* __restrict__ proj, long 
     dst[i + half] = from_f<T>(v * cs + u * sn);
   }
   for (int c = rot + lane; c < d; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv * (w ? w[c] : 1.f));
+  for (int c = d + lane; c < (is_q ? q_row : k_row); c += 32) dst[c] = from_f<T>(0.f);  // padding: adds nothing to a score
 }
 
 // One block per (token, query head).  The visible keys 0 .. pos are walked in chunks of SA_CHUNK with a running maximum / sum (fp32).
@@ -204,15 +207,18 @@ using namespace dsb::sinkattn;
 // [G dv] at v_col0.  Query / key heads: RMS norm over d with the weights wq / wk [d] (shared by the heads; null = no norm), then rotation
 // of the first rot_dims entries (pairs (i, i + rot_dims / 2)) by pos * freq[i] (freq: rot_dims / 2 doubles on the device) with cosine and
 // sine multiplied by `mag`.  Value heads: divided by their root mean square over dv when norm_v.  Queries -> q_out [T, q_ld]; keys ->
-// k_cache, values -> v_cache at the token's (block, slot) (see the file header for the plane addressing).
+// k_cache, values -> v_cache at the token's (block, slot) (see the file header for the plane addressing).  q_row / k_row / v_row: elements
+// between consecutive heads of a query row / a cached key row / a cached value row (>= d, d, dv); what lies past a head's own entries is
+// written as zeros, so that heads padded to a common width of 64 / 128 can be served by the tensor-core attention kernels.
 DSB_EXPORT int dsb200_head_norm_rotary_append(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* wq, const float* wk,
                                               const double* freq, float mag, const int* tok_seq, const int* tok_pos, const int* block_table,
                                               int bt_stride, int block_size, void* k_cache, long long k_block_stride, void* v_cache,
                                               long long v_block_stride, void* q_out, long long q_ld, int n_tokens, int H, int G, int d, int dv,
-                                              int rot_dims, float eps, int norm_v, int dtype, cudaStream_t stream) {
+                                              int rot_dims, float eps, int norm_v, int q_row, int k_row, int v_row, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
   DSB_REQUIRE(H >= 1 && G >= 1 && d >= 1 && dv >= 1 && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || freq != nullptr),
               "head_norm_rotary_append: heads %d / %d, head sizes %d / %d, rotated %d", H, G, d, dv, rot_dims);
+  DSB_REQUIRE(q_row >= d && k_row >= d && v_row >= dv, "head_norm_rotary_append: row widths %d / %d / %d below the head sizes %d / %d", q_row, k_row, v_row, d, dv);
   const long long warps = static_cast<long long>(n_tokens) * (H + 2 * G);
   const int wpb = 8;
   const int grid = static_cast<int>((warps + wpb - 1) / wpb);
@@ -220,12 +226,12 @@ DSB_EXPORT int dsb200_head_norm_rotary_append(const void* proj, long long ld, in
     head_norm_rotary_append_kernel<bf16><<<grid, wpb * 32, 0, stream>>>((const bf16*)proj, ld, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok_seq, tok_pos,
                                                                        block_table, bt_stride, block_size, (bf16*)k_cache, k_block_stride,
                                                                        (bf16*)v_cache, v_block_stride, (bf16*)q_out, q_ld, n_tokens, H, G, d, dv,
-                                                                       rot_dims, eps, norm_v);
+                                                                       rot_dims, eps, norm_v, q_row, k_row, v_row);
   else
     head_norm_rotary_append_kernel<float><<<grid, wpb * 32, 0, stream>>>((const float*)proj, ld, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok_seq,
                                                                         tok_pos, block_table, bt_stride, block_size, (float*)k_cache, k_block_stride,
                                                                         (float*)v_cache, v_block_stride, (float*)q_out, q_ld, n_tokens, H, G, d, dv,
-                                                                        rot_dims, eps, norm_v);
+                                                                        rot_dims, eps, norm_v, q_row, k_row, v_row);
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

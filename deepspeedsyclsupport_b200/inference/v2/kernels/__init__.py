@@ -497,7 +497,7 @@ native.register_sigs({
     "dsb200_delta_rule_scan": "ppppp p pp iiiii p",
     "dsb200_head_norm_gate": "pp i p l p l iii ff i p",
     "dsb200_tied_gate_scan": "p l iii pp p pp iiii i p",
-    "dsb200_head_norm_rotary_append": "p l iii pp p f ppp ii p l p l p l iiiii i f i i p",
+    "dsb200_head_norm_rotary_append": "p l iii pp p f ppp ii p l p l p l iiiii i f i iii i p",
     "dsb200_sink_attention": "p l p l p l ppp ii p l iiiii fff i p",
     "dsb200_paged_flash_sink": "p l pp l ppp iiiiiii fff ii p i p",
 }, restype_long=("dsb200_scan_state_floats", ))
@@ -659,10 +659,11 @@ def cache_planes(k_cache, v_cache=None):
 
 
 def head_norm_rotary_append(proj, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok_seq, tok_pos, block_table, block_size, k_plane, v_plane, q_out,
-                            H, G, d, dv, rot_dims, eps, norm_v=True):
+                            H, G, d, dv, rot_dims, eps, norm_v=True, row=None):
     """Per-head RMS norm (weights wq / wk [d], shared by the heads) and rotation of the first rot_dims entries (entry i with entry
     i + rot_dims / 2, angle pos * freq[i], cosine and sine times `mag`) of the query / key heads in columns q_col0 / k_col0 of proj; value
-    heads (columns v_col0) divided by their own root mean square when `norm_v`.  Queries -> q_out [T, >= H d]; keys / values -> their planes."""
+    heads (columns v_col0) divided by their own root mean square when `norm_v`.  Queries -> q_out [T, >= H d]; keys / values -> their planes.
+    `row`: every query head, cached key head and cached value head occupies this many entries (>= d and dv), zeros behind its own."""
     T = proj.shape[0]
     (kc, ks), (vc, vs) = k_plane, v_plane
     assert proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.dtype == proj.dtype == kc.dtype == vc.dtype
@@ -670,7 +671,8 @@ def head_norm_rotary_append(proj, q_col0, k_col0, v_col0, wq, wk, freq, mag, tok
                                                              native.ptr(freq), float(mag), native.ptr(tok_seq), native.ptr(tok_pos),
                                                              native.ptr(block_table), block_table.stride(0), int(block_size), native.ptr(kc), ks,
                                                              native.ptr(vc), vs, native.ptr(q_out), q_out.stride(0), T, H, G, d, dv, int(rot_dims),
-                                                             float(eps), int(norm_v), _dt(proj), native.stream_ptr()))
+                                                             float(eps), int(norm_v), int(row or d), int(row or d), int(row or dv), _dt(proj),
+                                                             native.stream_ptr()))
     return q_out
 
 

@@ -14,7 +14,8 @@ Every size may differ from layer to layer; all of them, the order of layers and 
 
 The class reuses the ragged engine's plumbing from `RaggedTransformer` (containers and streamed loading, decode-step CUDA graphs, the state
 manager's paged cache and block tables) and replaces the module set and the layer loop.  Attention layers get their cache tensors (one
-two-plane tensor, or a key and a value tensor when the head sizes differ), all sharing a sequence's block ids; the recurrent mixers' matrices
+two-plane tensor -- in bf16 of heads padded to a width the tensor-core kernels take -- or a key and a value tensor when the head sizes
+differ), all sharing a sequence's block ids; the recurrent mixers' matrices
 live in the state manager's per-sequence state slots, described by `state_config`.
 
 Fused steps: all projections that read a layer's normed input are ONE GEMM (mixer inputs | dense or shared-expert gate and up); the mixer's
@@ -272,10 +273,15 @@ class PudinexInferenceModel(RaggedTransformer, DSInferenceModelBase):
                 side_in, side_out = c["ff_in_w"], c["ff_down_w"]
             elif f is not None and f.shared_ff:
                 side_in, side_out = c["shared_in_w"], c["shared_down_w"]
+            o_w = c["o_w"]
+            if L.kind == "attention" and self.attn_mods[i].out_head_width != L.attn.vdim:
+                # the attention kernels work on heads padded to a common width: zero weights meet the (zero) padding columns of their output
+                P = self.attn_mods[i].out_head_width
+                o_w = torch.nn.functional.pad(o_w.view(o_w.shape[0], L.attn.heads, L.attn.vdim), (0, P - L.attn.vdim)).reshape(o_w.shape[0], L.attn.heads * P)
             if side_in is None:
-                self._fused[i] = (c["mix_in_w"], c["o_w"])
+                self._fused[i] = (c["mix_in_w"], o_w.contiguous())
             else:
-                self._fused[i] = (torch.cat([c["mix_in_w"], side_in], dim=0).contiguous(), torch.cat([c["o_w"], side_out], dim=1).contiguous())
+                self._fused[i] = (torch.cat([c["mix_in_w"], side_in], dim=0).contiguous(), torch.cat([o_w, side_out], dim=1).contiguous())
 
     # ---- forward
     def _side_hidden(self, L):
@@ -303,7 +309,7 @@ class PudinexInferenceModel(RaggedTransformer, DSInferenceModelBase):
             side = self._side_hidden(L)
             if L.kind == "attention":
                 a = L.attn
-                n_mix_in, n_mix_out = (a.heads + a.kv_heads) * a.dim + a.kv_heads * a.vdim, a.heads * a.vdim
+                n_mix_in, n_mix_out = (a.heads + a.kv_heads) * a.dim + a.kv_heads * a.vdim, self.attn_mods[li].out_width
             else:
                 g = L.gate
                 n_mix_in, n_mix_out = g.heads * (2 * g.dim + g.vdim), g.heads * g.vdim

@@ -6,9 +6,11 @@ cache), then the attention kernel.  Query / key heads and value heads may differ
 [blocks, 2, block_size, kv_heads, head_size] tensor, otherwise two single-plane tensors [blocks, block_size, kv_heads, size] that share the
 block ids.  csrc/ragged/sink_attention_ops.cu.
 
-Two attention kernels.  bf16 with equal head sizes of 64 / 128: the tcgen05 paged flash kernels (csrc/attn/paged_flash.cu) with the soft cap
-and the sink.  Everything else (fp32, other or unequal head sizes): `sink_attention`, a CUDA-core kernel with fp32 scores and accumulation
-that takes any size."""
+Two attention kernels.  bf16 with head sizes up to 128: the tcgen05 paged flash kernels (csrc/attn/paged_flash.cu) with the soft cap and the
+sink.  They want one head size of 64 or 128 for queries, keys and values, so every head is PADDED to that width with zeros (a zero entry of
+a query / key adds nothing to a score; a zero column of the values gives a zero column of the output, which the output projection meets
+with zero weights): the layer's cache is then one two-plane tensor of the padded width and `out_width` is heads x padded width.  Everything
+else (fp32, head sizes above 128): `sink_attention`, a CUDA-core kernel with fp32 scores and accumulation that takes any sizes."""
 import math
 from typing import Any, Dict, Optional, Type
 
@@ -61,6 +63,9 @@ class DSSinkBlockedAttention(DSSelfAttentionBase):
         self._dtype = DtypeEnum(config.input_dtype).value
         self._freq_host, self._mag = ramp_scaled_frequencies(config.rotate_dim, config.theta_base, config.rotary_scaling)
         self._freq = None
+        # common width of all heads on the tensor-core path (None: every head keeps its own size)
+        widest = max(config.head_size, config.value_size)
+        self._pad = (64 if widest <= 64 else 128) if (self._dtype == torch.bfloat16 and widest <= 128) else None
 
     @property
     def kv_block_size(self) -> int:
@@ -73,9 +78,20 @@ class DSSinkBlockedAttention(DSSelfAttentionBase):
     def cache_shapes(self):
         """(planes, heads, width) of the cache tensors this layer needs, in the order `forward` takes them."""
         c = self._config
+        if self._pad is not None:
+            return [(2, c.n_heads_kv, self._pad)]
         if c.head_size == c.value_size:
             return [(2, c.n_heads_kv, c.head_size)]
         return [(1, c.n_heads_kv, c.head_size), (1, c.n_heads_kv, c.value_size)]
+
+    @property
+    def out_head_width(self) -> int:
+        """Entries per head of the attention output (the value size, or the padded width)."""
+        return self._pad if self._pad is not None else self._config.value_size
+
+    @property
+    def out_width(self) -> int:
+        return self._config.n_heads_q * self.out_head_width
 
     def transform_fp32_param(self, param: torch.Tensor) -> InferenceParameter:
         """The norm weights stay fp32."""
@@ -84,7 +100,7 @@ class DSSinkBlockedAttention(DSSelfAttentionBase):
     def forward(self, proj: torch.Tensor, cols, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], batch, norm_q: Optional[torch.Tensor],
                 norm_k: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         """proj [T, N]: the fused projection with queries, keys and values at the columns cols = (q, k, v).  k_cache / v_cache: the layer's
-        cache tensor(s) as `cache_shapes` lists them (v_cache None for the two-plane tensor).  out: [T, heads * value_size] view."""
+        cache tensor(s) as `cache_shapes` lists them (v_cache None for the two-plane tensor).  out: [T, out_width] view."""
         c = self._config
         q0, k0, v0 = cols
         H, G, d, dv = c.n_heads_q, c.n_heads_kv, c.head_size, c.value_size
@@ -92,10 +108,13 @@ class DSSinkBlockedAttention(DSSelfAttentionBase):
             self._freq = self._freq_host.to(proj.device)
         kp, vp = K.cache_planes(k_cache, v_cache)
         bs = k_cache.shape[2] if v_cache is None else k_cache.shape[1]
-        q = torch.empty(proj.shape[0], H * d, dtype=proj.dtype, device=proj.device)
+        P = self._pad
+        q = torch.empty(proj.shape[0], H * (P or d), dtype=proj.dtype, device=proj.device)
         K.head_norm_rotary_append(proj, q0, k0, v0, norm_q if c.qk_norm else None, norm_k if c.qk_norm else None, self._freq if c.rotate_dim else None,
                                   self._mag, batch.tok_seq(), batch.tok_pos(), batch.block_table(), bs, kp, vp, q, H, G, d, dv, c.rotate_dim, c.eps,
-                                  norm_v=c.v_norm)
+                                  norm_v=c.v_norm, row=P)
+        if P is not None:
+            d = dv = P  # from here on every head is P wide
         if v_cache is None and K.paged_flash_sink_ok(q, k_cache, out, H, G, d, dv):
             return K.paged_flash_sink(q, k_cache, batch.tok_seq(), batch.tok_pos(), batch.block_table(), out, H, G, d, c.scale, c.softcap, c.sink,
                                       decode=batch.current_tokens <= 2 * batch.current_sequences)

@@ -555,13 +555,15 @@ int dsb200_head_norm_gate(const float* o, const float* w, int w_stride, const vo
  * [G dv] at v_col0.  Query / key heads: RMS norm over d with the weights wq / wk [d] (shared by the heads; null = no norm), then rotation
  * of the first rot_dims entries (pairs (i, i + rot_dims / 2)) by pos * freq[i] (freq: rot_dims / 2 doubles on the device) with cosine and
  * sine multiplied by `mag`.  Value heads: divided by their root mean square over dv when norm_v.  Queries -> q_out [T, q_ld]; keys ->
- * k_cache, values -> v_cache at the token's (block, slot) (see the file header for the plane addressing). */
+ * k_cache, values -> v_cache at the token's (block, slot) (see the file header for the plane addressing).  q_row / k_row / v_row: elements
+ * between consecutive heads of a query row / a cached key row / a cached value row (>= d, d, dv); what lies past a head's own entries is
+ * written as zeros, so that heads padded to a common width of 64 / 128 can be served by the tensor-core attention kernels. */
 int dsb200_head_norm_rotary_append(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* wq,
                                    const float* wk, const double* freq, float mag, const int* tok_seq, const int* tok_pos,
                                    const int* block_table, int bt_stride, int block_size, void* k_cache,
                                    long long k_block_stride, void* v_cache, long long v_block_stride, void* q_out,
                                    long long q_ld, int n_tokens, int H, int G, int d, int dv, int rot_dims, float eps,
-                                   int norm_v, int dtype, dsb200_stream_t stream);
+                                   int norm_v, int q_row, int k_row, int v_row, int dtype, dsb200_stream_t stream);
 /* out[t, h dv + c] = sum_j p_j v_j[c] over the keys j <= pos(t) of the token's sequence, p_j = exp(s_j) / (sink + sum_j exp(s_j)),
  * s_j = scale q_h . k_j, soft-capped as cap tanh(s_j / cap) when cap > 0.  q [T, q_ld] (H heads of d); query head h reads key/value head
  * h / (H / G); out [T, out_ld] (H heads of dv).  CUDA cores, fp32 scores and accumulation, any sizes; dtype 0 = bf16, 1 = fp32. */

@@ -78,6 +78,24 @@ def test_cache_state_and_fused_weights_of_a_model():
             build_model_from_checkpoint("pudinex", cfg, InMemoryModelEngine(w2), None, device=torch.device("cpu"), dtype=torch.float32)
 
 
+def test_bf16_attention_heads_are_padded_to_a_tensor_core_width():
+    """bf16: keys and values of any sizes up to 128 share one two-plane cache tensor of width 64 / 128 and the output projection gets zero
+    columns for the padding; fp32 and wider heads keep their own sizes."""
+    from deepspeedsyclsupport_b200.inference.v2.checkpoint import InMemoryModelEngine
+    from deepspeedsyclsupport_b200.inference.v2.engine_factory import build_model_from_checkpoint
+    cfg = O.make_config([O.attention_layer(4, 2, 6, 10, mlp=O.dense(8)), O.attention_layer(2, 1, 96, 40), O.attention_layer(2, 2, 64, 64), O.attention_layer(1, 1, 130, 20)],
+                        width=24)
+    w = O.random_weights(cfg)
+    m = build_model_from_checkpoint("pudinex", cfg, InMemoryModelEngine(w), None, device=torch.device("cpu"), dtype=torch.bfloat16)
+    assert m.kv_cache_config(block_size=16).layer_shapes == [(2, 2, 64), (2, 1, 128), (2, 2, 64), (1, 1, 130), (1, 1, 20)]
+    assert [a.out_head_width for a in m.attn_mods] == [64, 128, 64, 20]
+    w_out = m._fused[0][1]
+    assert w_out.shape == (24, 4 * 64 + 8)
+    per_head = w_out[:, :4 * 64].view(24, 4, 64)
+    assert torch.equal(per_head[:, :, :10].reshape(24, 40), w["l0.mix.o"]) and float(per_head[:, :, 10:].abs().max()) == 0
+    assert torch.equal(w_out[:, 4 * 64:], w["l0.mlp.down"])
+
+
 def test_router_with_identity_experts_is_served_by_the_grouped_router():
     from deepspeedsyclsupport_b200.inference.v2.inference_utils import ActivationType, DtypeEnum
     from deepspeedsyclsupport_b200.inference.v2.modules import heuristics
@@ -239,10 +257,13 @@ def test_attention_mixer(case, sizes, dt):
     outs = []
     for at, n in _cuts(T, sizes):
         proj = (h[at:at + n] @ Win.T).to(dt).cuda()
-        out = torch.empty(n, H * dv, dtype=dt, device="cuda")
+        out = torch.empty(n, mod.out_width, dtype=dt, device="cuda")
         mod(proj, (0, H * d, (H + G) * d), caches[0], caches[1] if len(caches) > 1 else None, _Batch([(0, at, n, pages)], 16),
             w["q.norm"].float().cuda(), w["k.norm"].float().cuda(), out)
-        outs.append(out)
+        per_head = out.view(n, H, mod.out_head_width)
+        if mod.out_head_width > dv:  # the padding columns of a head stay empty (a masked key of a garbage page may leave ~1e-37 there)
+            assert float(per_head[:, :, dv:].abs().max()) < 1e-30
+        outs.append(per_head[:, :, :dv].reshape(n, H * dv))
     assert _rel(torch.cat(outs), want) < (2e-5 if dt == torch.float32 else 2.5e-2)
 
 
