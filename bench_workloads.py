@@ -875,8 +875,9 @@ def _pudinex_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, T, ctx, n_dec)
         oh = torch.empty(Tn, H * d // 2, device=dev, dtype=bf)
         add(f"attention, soft cap 50 + sink, CUDA cores, values {d // 2} wide, {label}",
             _event_ms(torch, lambda: K.sink_attention(qo, kp, vp, tok_seq, tok_pos, bt, bs, oh, H, hkv, d, d // 2, d ** -0.5, 50.0, 1.0), 3, flush),
-            f"paged flash attention, causal, {label} (Mixtral)", rows[-1]["like_ms"], nbytes=n_seq * (seen + new) * hkv * d * 3 + Tn * H * d * 3,
-            like_bytes=abytes, flops=3.0 * keys * H * d, like_flops=4.0 * keys * H * d)
+            f"window_attention, CUDA cores, window covering the context (Kulanex), {label}",
+            _event_ms(torch, lambda: K.window_attention(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, 1 << 30, 0, d ** -0.5), 3, flush),
+            nbytes=n_seq * (seen + new) * hkv * d * 3 + Tn * H * d * 3, like_bytes=abytes, flops=3.0 * keys * H * d, like_flops=4.0 * keys * H * d)
         # recurrent scan beside Kulanex's delta rule on a state of the same size
         proj = torch.randn(Tn, 3 * H * d, device=dev).to(bf)
         fb, lo = torch.full((H * d, ), 2.0, device=dev), torch.full((H * d, ), 0.5, device=dev)
