@@ -233,6 +233,8 @@ ATTENTION_CASES = [
     dict(heads=3, kv_heads=1, dim=14, vdim=20, softcap=25.0),  # one key / value head, no rotation, values wider than keys
     dict(heads=4, kv_heads=4, dim=64, vdim=32, softcap=10.0, rot=dict(dims=32, base=1e5, scaling={"factor": 3.0, "original": 64, "fast": 8.0, "slow": 2.0})),
     dict(heads=1, kv_heads=1, dim=5, vdim=3, softcap=1.0, rot=dict(dims=2, base=10.0)),  # one head, a tight cap
+    dict(heads=2, kv_heads=2, dim=32, vdim=96, softcap=15.0, rot=dict(dims=16, base=1000.0)),  # values wider than keys, padded to 128 in bf16
+    dict(heads=2, kv_heads=1, dim=136, vdim=40, softcap=8.0, rot=dict(dims=136, base=1e4)),  # heads above 128: the CUDA-core kernel in bf16 too
 ]
 
 
