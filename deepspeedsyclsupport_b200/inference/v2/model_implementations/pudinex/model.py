@@ -313,7 +313,8 @@ class PudinexInferenceModel(RaggedTransformer, DSInferenceModelBase):
             else:
                 g = L.gate
                 n_mix_in, n_mix_out = g.heads * (2 * g.dim + g.vdim), g.heads * g.vdim
-            mixed = torch.empty(h.shape[0], n_mix_out + side, dtype=h.dtype, device=h.device)  # [mixer output | activated hidden]
+            # [mixer output | activated hidden]; rows start 16 bytes apart at least (what the tensor-core attention's stores want) whatever the sizes
+            mixed = torch.empty(h.shape[0], -(-(n_mix_out + side) // 8) * 8, dtype=h.dtype, device=h.device)[:, :n_mix_out + side]
             if L.kind == "attention":
                 caches = [state_manager.get_cache(ci) for ci in self._cache_index[li]]
                 self.attn_mods[li](proj, (0, a.heads * a.dim, (a.heads + a.kv_heads) * a.dim), caches[0], caches[1] if len(caches) > 1 else None, batch,
