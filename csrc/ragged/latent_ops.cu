@@ -1141,3 +1141,149 @@ DSB_EXPORT int dsb200_moe_gemm_rows(const void* x, const void* w, void* out, con
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }
+
+// ------------------------------------------------------------------------------------------- norm behind the sum, xIELU, scalar head gates
+//   post_sum_norm         x <- rms(alpha x + y + y32 + bias) * w on the fp32 stream (blocks whose norm sits BEHIND the residual sum), with a
+//                         copy of the new stream in the activation dtype for the sublayer that reads it next
+//   xielu                 z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2   (a, b read from device memory)
+//   gate_heads_scalar     head-major result of a per-head batched GEMM -> token-major heads, each multiplied by the sigmoid of ONE number
+namespace dsb {
+namespace latent {
+
+// One block per row.  VEC: dim % 4 == 0 and 16-byte aligned rows; the row is then walked in 4-value accesses.
+template <typename TY, typename TO, bool VEC>
+__global__ void post_sum_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ y32, const float* __restrict__ bias,
+                                     const float* __restrict__ w, TO* __restrict__ out, int dim, float alpha, float eps) {
+  __shared__ float red[33];
+  const size_t r = blockIdx.x;
+  float* xr = x + r * dim;
+  const TY* yr = y ? y + r * dim : nullptr;
+  const float* zr = y32 ? y32 + r * dim : nullptr;
+  TO* orow = out ? out + r * dim : nullptr;
+  float ss = 0.f;
+  if constexpr (VEC) {
+    for (int c = 4 * threadIdx.x; c < dim; c += 4 * blockDim.x) {
+      float4 s = load4(xr + c);
+      s.x *= alpha; s.y *= alpha; s.z *= alpha; s.w *= alpha;
+      if (yr) { const float4 v = load4(yr + c); s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+      if (zr) { const float4 v = load4(zr + c); s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+      if (bias) { const float4 v = load4(bias + c); s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+      store4(xr + c, s);
+      ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    }
+  } else {
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      float s = alpha * xr[c];
+      if (yr) s += to_f(yr[c]);
+      if (zr) s += zr[c];
+      if (bias) s += bias[c];
+      xr[c] = s;
+      ss += s * s;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(dim) + eps);
+  if constexpr (VEC) {  // every thread meets the values it wrote itself
+    for (int c = 4 * threadIdx.x; c < dim; c += 4 * blockDim.x) {
+      float4 s = load4(xr + c);
+      const float4 g = load4(w + c);
+      s.x = s.x * inv * g.x; s.y = s.y * inv * g.y; s.z = s.z * inv * g.z; s.w = s.w * inv * g.w;
+      store4(xr + c, s);
+      if (orow) store4(orow + c, s);
+    }
+  } else {
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float v = xr[c] * inv * w[c];
+      xr[c] = v;
+      if (orow) orow[c] = from_f<TO>(v);
+    }
+  }
+}
+
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ u, long long ld, T* __restrict__ out, long long rows, int F, const float* __restrict__ coef) {
+  const float a = coef[0], b = coef[1];
+  const long long n = rows * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float z = to_f(u[(i / F) * ld + (i % F)]);
+    out[i] = from_f<T>(z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z));
+  }
+}
+template <typename T>
+__global__ void xielu_vec_kernel(const T* __restrict__ u, T* __restrict__ out, long long n4, const float* __restrict__ coef) {
+  const float a = coef[0], b = coef[1];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 z = load4(u + 4 * i);
+    z.x = z.x > 0.f ? fmaf(a * z.x, z.x, 0.5f * z.x) : fmaf(b, expm1f(z.x) - z.x, 0.5f * z.x);
+    z.y = z.y > 0.f ? fmaf(a * z.y, z.y, 0.5f * z.y) : fmaf(b, expm1f(z.y) - z.y, 0.5f * z.y);
+    z.z = z.z > 0.f ? fmaf(a * z.z, z.z, 0.5f * z.z) : fmaf(b, expm1f(z.z) - z.z, 0.5f * z.z);
+    z.w = z.w > 0.f ? fmaf(a * z.w, z.w, 0.5f * z.w) : fmaf(b, expm1f(z.w) - z.w, 0.5f * z.w);
+    store4(out + 4 * i, z);
+  }
+}
+
+template <typename T>
+__global__ void gate_heads_scalar_kernel(const T* __restrict__ a, const T* __restrict__ g, long long g_ld, T* __restrict__ out, long long out_ld,
+                                         int n_tokens, int H, int dv) {
+  const int row = H * dv;
+  const long long n = static_cast<long long>(n_tokens) * row;
+  for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < n; e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = e / row;
+    const int rem = static_cast<int>(e % row), h = rem / dv, c = rem % dv;
+    const float gate = 1.f / (1.f + expf(-to_f(g[t * g_ld + h])));
+    out[t * out_ld + rem] = from_f<T>(to_f(a[(static_cast<long long>(h) * n_tokens + t) * dv + c]) * gate);
+  }
+}
+
+}  // namespace latent
+}  // namespace dsb
+
+// x [rows, dim] fp32, in place: x <- s / sqrt(mean(s^2) + eps) * w with s = alpha x + y + y32 + bias; y [rows, dim] in y_dtype (0 = bf16,
+// 1 = fp32), y32 [rows, dim] fp32, bias [dim] fp32 -- each may be null.  out (null, or [rows, dim] in out_dtype): the new x, rounded.
+DSB_EXPORT int dsb200_post_sum_norm(float* x, const void* y, int y_dtype, const float* y32, const float* bias, const float* w, void* out, int out_dtype,
+                                    long long rows, int dim, float alpha, float eps, cudaStream_t stream) {
+  if (rows == 0) return DSB_OK;
+  DSB_REQUIRE(x != nullptr && w != nullptr && dim >= 1, "post_sum_norm: stream / weight missing or width %d", dim);
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = dim % 8 == 0 && al(x) && al(y) && al(y32) && al(bias) && al(w) && al(out);
+  const int threads = vec ? (dim >= 4096 ? 512 : (dim >= 1024 ? 256 : 128)) : 256;
+  const unsigned grid = static_cast<unsigned>(rows);
+#define LAUNCH(TY, TO)                                                                                                                          \
+  do {                                                                                                                                          \
+    if (vec) post_sum_norm_kernel<TY, TO, true><<<grid, threads, 0, stream>>>(x, (const TY*)y, y32, bias, w, (TO*)out, dim, alpha, eps);        \
+    else post_sum_norm_kernel<TY, TO, false><<<grid, threads, 0, stream>>>(x, (const TY*)y, y32, bias, w, (TO*)out, dim, alpha, eps);           \
+  } while (0)
+  if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
+  else if (y_dtype == 0) LAUNCH(bf16, float);
+  else if (out_dtype == 0) LAUNCH(float, bf16);
+  else LAUNCH(float, float);
+#undef LAUNCH
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out [rows, F] = xIELU(u [rows, ld]): z > 0: coef[0] z^2 + z / 2; z <= 0: coef[1] (exp(z) - 1 - z) + z / 2; coef: two floats on the device.
+DSB_EXPORT int dsb200_xielu(const void* u, long long ld, void* out, long long rows, int F, const float* coef, int dtype, cudaStream_t stream) {
+  const long long n = rows * F;
+  if (n == 0) return DSB_OK;
+  DSB_REQUIRE(coef != nullptr && ld >= F, "xielu: coefficients missing or row stride %lld below %d", ld, F);
+  const bool vec = ld == F && n % 4 == 0 && ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (vec && dtype == 0) xielu_vec_kernel<bf16><<<grid_for(n / 4, 256), 256, 0, stream>>>((const bf16*)u, (bf16*)out, n / 4, coef);
+  else if (vec) xielu_vec_kernel<float><<<grid_for(n / 4, 256), 256, 0, stream>>>((const float*)u, (float*)out, n / 4, coef);
+  else if (dtype == 0) xielu_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)u, ld, (bf16*)out, rows, F, coef);
+  else xielu_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)u, ld, (float*)out, rows, F, coef);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out[t, h dv + c] = a[h, t, c] * sigmoid(g[t, h]): a [H, n_tokens, dv] contiguous, g [n_tokens, g_ld] with one number per head.
+DSB_EXPORT int dsb200_gate_heads_scalar(const void* a, const void* g, long long g_ld, void* out, long long out_ld, int n_tokens, int H, int dv,
+                                        int dtype, cudaStream_t stream) {
+  const long long n = static_cast<long long>(n_tokens) * H * dv;
+  if (n == 0) return DSB_OK;
+  DSB_REQUIRE(out_ld >= static_cast<long long>(H) * dv && g_ld >= H, "gate_heads_scalar: strides %lld / %lld", out_ld, g_ld);
+  if (dtype == 0) gate_heads_scalar_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)a, (const bf16*)g, g_ld, (bf16*)out, out_ld, n_tokens, H, dv);
+  else gate_heads_scalar_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)a, (const float*)g, g_ld, (float*)out, out_ld, n_tokens, H, dv);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}

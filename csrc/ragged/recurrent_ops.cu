@@ -1080,3 +1080,164 @@ DSB_EXPORT int dsb200_head_norm_gate(const float* o, const float* w, int w_strid
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }
+
+// ------------------------------------------------------------------------------------------------------------------ minimal gated recurrence
+// One number of state per channel: S <- (1 - z) S + z c with z = sigmoid(pz + bz), u = px + bx, c = u + 1/2 for u >= 0 and sigmoid(u) below;
+// out = S silu(pg).  pz, px, pg are columns of the fused projection.  The update is the affine map S -> a S + b with a = 1 - z, b = z c, and
+// affine maps compose, so long portions are cut into pieces of MG_PIECE rows of the BATCH (a piece may hold the end of one sequence and the
+// start of the next: the first row of a sequence replaces whatever came before by the sequence's stored state, or zero at position 0):
+//   mingru_scan_kernel     one thread per (sequence, channel) walks the new tokens in order (decode steps and short portions)
+//   mingru_pieces_kernel   per (piece, channel): the composed map of the piece, (A, B); a sequence start inside makes A = 0
+//   mingru_carry_kernel    per channel: walks the pieces, leaves the state in front of every piece
+//   mingru_apply_kernel    per (piece, channel): walks the piece again from its carry, writes the outputs and, at a sequence's last row, its state
+namespace dsb {
+namespace recur {
+
+constexpr int MG_PIECE = 32;
+
+struct MinGruIn {
+  float a, b, g;
+};
+template <typename T>
+__device__ __forceinline__ MinGruIn mingru_load(const T* __restrict__ row, int z0, int x0, int g0, int c, float bz, float bx) {
+  const float z = sigmoidf_(to_f(row[z0 + c]) + bz);
+  const float u = to_f(row[x0 + c]) + bx;
+  MinGruIn r;
+  r.a = 1.f - z;
+  r.b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+  r.g = to_f(row[g0 + c]);
+  return r;
+}
+
+template <typename T>
+__global__ void mingru_scan_kernel(const T* __restrict__ proj, long long ld, int z0, int x0, int g0, const float* __restrict__ zb,
+                                   const float* __restrict__ xb, const int4* __restrict__ seq_desc, float* __restrict__ state,
+                                   T* __restrict__ out, long long out_ld, int W) {
+  const int4 sd = seq_desc[blockIdx.y];
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  float* st = state + static_cast<size_t>(sd.w) * W + c;
+  float S = sd.z > 0 ? *st : 0.f;  // a sequence at position 0 starts from zero whatever the slot held
+  const float bz = zb[c], bx = xb[c];
+  const T* row = proj + static_cast<long long>(sd.x) * ld;
+  T* o = out + static_cast<long long>(sd.x) * out_ld + c;
+  for (int i = 0; i < sd.y; ++i, row += ld, o += out_ld) {
+    const MinGruIn in = mingru_load(row, z0, x0, g0, c, bz, bx);
+    S = fmaf(in.a, S, in.b);
+    *o = from_f<T>(S * siluf_(in.g));
+  }
+  *st = S;
+}
+
+// start[t]: -1 inside a sequence, else the index of the sequence whose first new token is row t.
+template <typename T>
+__global__ void mingru_pieces_kernel(const T* __restrict__ proj, long long ld, int z0, int x0, const float* __restrict__ zb,
+                                     const float* __restrict__ xb, const int* __restrict__ tok_seq, const int4* __restrict__ seq_desc,
+                                     const float* __restrict__ state, float* __restrict__ init, float* __restrict__ pa, float* __restrict__ pb,
+                                     int n_tokens, int W) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const int p = blockIdx.y, t0 = p * MG_PIECE, t1 = min(n_tokens, t0 + MG_PIECE);
+  const float bz = zb[c], bx = xb[c];
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const int s = tok_seq[t];
+    const int4 sd = seq_desc[s];
+    if (t == sd.x) {  // the sequence's own state replaces what came before
+      const float S0 = sd.z > 0 ? state[static_cast<size_t>(sd.w) * W + c] : 0.f;
+      init[static_cast<size_t>(s) * W + c] = S0;
+      A = 0.f;
+      B = S0;
+    }
+    const T* row = proj + static_cast<long long>(t) * ld;
+    const float z = sigmoidf_(to_f(row[z0 + c]) + bz);
+    const float u = to_f(row[x0 + c]) + bx;
+    const float a = 1.f - z, b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+    A *= a;
+    B = fmaf(a, B, b);
+  }
+  pa[static_cast<size_t>(p) * W + c] = A;
+  pb[static_cast<size_t>(p) * W + c] = B;
+}
+
+__global__ void mingru_carry_kernel(const float* __restrict__ pa, float* __restrict__ pb, int n_pieces, int W) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  float S = 0.f;  // row 0 starts a sequence, so the first piece has A = 0
+  for (int p = 0; p < n_pieces; ++p) {
+    const size_t i = static_cast<size_t>(p) * W + c;
+    const float A = pa[i], B = pb[i];
+    pb[i] = S;  // the state in front of piece p
+    S = fmaf(A, S, B);
+  }
+}
+
+template <typename T>
+__global__ void mingru_apply_kernel(const T* __restrict__ proj, long long ld, int z0, int x0, int g0, const float* __restrict__ zb,
+                                    const float* __restrict__ xb, const int* __restrict__ tok_seq, const int4* __restrict__ seq_desc,
+                                    float* __restrict__ state, const float* __restrict__ init, const float* __restrict__ carry,
+                                    T* __restrict__ out, long long out_ld, int n_tokens, int W) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const int p = blockIdx.y, t0 = p * MG_PIECE, t1 = min(n_tokens, t0 + MG_PIECE);
+  const float bz = zb[c], bx = xb[c];
+  float S = carry[static_cast<size_t>(p) * W + c];
+  for (int t = t0; t < t1; ++t) {
+    const int s = tok_seq[t];
+    const int4 sd = seq_desc[s];
+    if (t == sd.x) S = init[static_cast<size_t>(s) * W + c];
+    const MinGruIn in = mingru_load(proj + static_cast<long long>(t) * ld, z0, x0, g0, c, bz, bx);
+    S = fmaf(in.a, S, in.b);
+    out[static_cast<long long>(t) * out_ld + c] = from_f<T>(S * siluf_(in.g));
+    if (t == sd.x + sd.y - 1) state[static_cast<size_t>(sd.w) * W + c] = S;
+  }
+}
+
+}  // namespace recur
+}  // namespace dsb
+
+DSB_EXPORT long long dsb200_mingru_scratch_floats(int n_tokens, int n_seqs, int W) {
+  const long long pieces = (n_tokens + dsb::recur::MG_PIECE - 1) / dsb::recur::MG_PIECE;
+  return (2 * pieces + n_seqs) * static_cast<long long>(W);
+}
+
+// Minimal gated recurrence over every sequence's new tokens.  proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds the gate, candidate and output-gate
+// pre-activations at columns z_col0 / x_col0 / g_col0 (W each); zb, xb fp32 [W]; state fp32 [slots, W]; out [T, out_ld] in proj's dtype.
+// seq_desc [n_seqs, 4] = (first row, new tokens, tokens seen before, slot); tok_seq [T].  scratch: dsb200_mingru_scratch_floats floats, used
+// when `pieces` != 0 (portions cut into pieces that are walked side by side); else one thread per (sequence, channel) walks its tokens.
+DSB_EXPORT int dsb200_mingru_scan(const void* proj, long long ld, int z_col0, int x_col0, int g_col0, const float* zb, const float* xb,
+                                  const int* tok_seq, const int* seq_desc, float* state, void* out, long long out_ld, int n_tokens, int n_seqs, int W,
+                                  int pieces, float* scratch, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0 || n_seqs == 0) return DSB_OK;
+  DSB_REQUIRE(W >= 1 && out_ld >= W && zb != nullptr && xb != nullptr && state != nullptr, "mingru_scan: width %d, output stride %lld", W, out_ld);
+  const int threads = 128;
+  const unsigned gx = static_cast<unsigned>((W + threads - 1) / threads);
+  if (!pieces) {
+    const dim3 grid(gx, n_seqs);
+    if (dtype == 0)
+      mingru_scan_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (bf16*)out, out_ld, W);
+    else
+      mingru_scan_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (float*)out, out_ld, W);
+    DSB_CHECK_CUDA(cudaGetLastError());
+    return DSB_OK;
+  }
+  DSB_REQUIRE(scratch != nullptr && tok_seq != nullptr, "mingru_scan: the piecewise walk needs its scratch and the token -> sequence map");
+  const int np = (n_tokens + MG_PIECE - 1) / MG_PIECE;
+  float* pa = scratch;
+  float* pb = pa + static_cast<size_t>(np) * W;
+  float* init = pb + static_cast<size_t>(np) * W;
+  const dim3 grid(gx, np);
+  if (dtype == 0)
+    mingru_pieces_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
+  else
+    mingru_pieces_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
+  mingru_carry_kernel<<<gx, threads, 0, stream>>>(pa, pb, np, W);
+  if (dtype == 0)
+    mingru_apply_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb,
+                                                           (bf16*)out, out_ld, n_tokens, W);
+  else
+    mingru_apply_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb,
+                                                            (float*)out, out_ld, n_tokens, W);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}

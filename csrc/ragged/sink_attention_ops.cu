@@ -135,14 +135,26 @@ __global__ void head_norm_rotary_append_kernel(const T* __restrict__ proj, long 
   for (int c = d + lane; c < (is_q ? q_row : k_row); c += 32) dst[c] = from_f<T>(0.f);  // padding: adds nothing to a score
 }
 
-// One block per (token, query head).  The visible keys 0 .. pos are walked in chunks of SA_CHUNK with a running maximum / sum (fp32).
+// What the plain form of `sink_attention` does not have: per-head sink scores, a distance term on the scores, a mask by fixed parts of the
+// sequence, and strides of their own for query / output heads and cached rows (so that one cached row can serve as key and as value).
+struct SinkExtras {
+  const float* sink_logit;     // [H] or null: exp(sink_logit[h]) joins the denominator (an entry without key and value)
+  const float* r1;             // [H] or null: the score of key j loses r1[h] ln(1 + r2[h] (pos - j))
+  const float* r2;
+  int part;                    // > 0: a query at pos sees only the keys j <= pos with j / part == pos / part
+  int k_row, v_row;            // elements between the heads of a cached key row / value row (>= d, dv)
+  long long q_head_stride;     // elements between the heads of a query row
+  long long out_head_stride;   // elements between the heads of an output row
+};
+
+// One block per (token, query head).  The visible keys first .. pos are walked in chunks of SA_CHUNK with a running maximum / sum (fp32).
 constexpr int SA_CHUNK = 256, SA_THREADS = 128;
 template <typename T>
 __global__ void __launch_bounds__(SA_THREADS)
 sink_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __restrict__ k_cache, long long k_block_stride,
                       const T* __restrict__ v_cache, long long v_block_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ out, long long out_ld, int H, int G,
-                      int d, int dv, float scale, float cap, float sink) {
+                      int d, int dv, float scale, float cap, float sink, SinkExtras ex) {
   extern __shared__ float sm[];
   __shared__ float red[33];
   __shared__ float sc[SA_CHUNK];
@@ -151,14 +163,17 @@ sink_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __restri
   const int seq = tok_seq[t], pos = tok_pos[t];
   float* qs = sm;        // [d]
   float* acc = sm + d;   // [dv]
-  for (int c = threadIdx.x; c < d; c += SA_THREADS) qs[c] = to_f(q[static_cast<long long>(t) * q_ld + h * d + c]) * scale;
+  for (int c = threadIdx.x; c < d; c += SA_THREADS) qs[c] = to_f(q[static_cast<long long>(t) * q_ld + h * ex.q_head_stride + c]) * scale;
   for (int c = threadIdx.x; c < dv; c += SA_THREADS) acc[c] = 0.f;
   const int n = pos + 1;
+  const int first = ex.part > 0 ? (pos / ex.part) * ex.part : 0;
   const int* bt = block_table + static_cast<size_t>(seq) * bt_stride;
   const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
+  const float r1 = ex.r1 ? ex.r1[h] : 0.f, r2 = ex.r1 ? ex.r2[h] : 0.f;
+  // a learned sink starts the running softmax as an entry of its own: maximum = its score, sum = 1, nothing accumulated
+  float m_run = ex.sink_logit ? ex.sink_logit[h] : -INFINITY, l_run = ex.sink_logit ? 1.f : 0.f;
   __syncthreads();
-  for (int x0 = 0; x0 < n; x0 += SA_CHUNK) {
+  for (int x0 = first; x0 < n; x0 += SA_CHUNK) {
     const int cn = min(SA_CHUNK, n - x0);
     float mx = -INFINITY;
     for (int x = threadIdx.x; x < cn; x += SA_THREADS) {
@@ -166,10 +181,11 @@ sink_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __restri
       const int blk = bt[j / block_size], slot = j % block_size;
       key_blk[x] = blk;
       key_slot[x] = slot;
-      const T* kr = k_cache + static_cast<long long>(blk) * k_block_stride + (static_cast<long long>(slot) * G + g) * d;
+      const T* kr = k_cache + static_cast<long long>(blk) * k_block_stride + (static_cast<long long>(slot) * G + g) * ex.k_row;
       float s = 0.f;
       for (int c = 0; c < d; ++c) s = fmaf(qs[c], to_f(kr[c]), s);
       if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+      if (ex.r1) s -= r1 * log1pf(r2 * static_cast<float>(pos - j));
       sc[x] = s;
       mx = fmaxf(mx, s);
     }
@@ -188,13 +204,126 @@ sink_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __restri
     for (int c = threadIdx.x; c < dv; c += SA_THREADS) {
       float a = acc[c] * corr;
       for (int x = 0; x < cn; ++x)
-        a = fmaf(sc[x], to_f(v_cache[static_cast<long long>(key_blk[x]) * v_block_stride + (static_cast<long long>(key_slot[x]) * G + g) * dv + c]), a);
+        a = fmaf(sc[x], to_f(v_cache[static_cast<long long>(key_blk[x]) * v_block_stride + (static_cast<long long>(key_slot[x]) * G + g) * ex.v_row + c]), a);
       acc[c] = a;
     }
     __syncthreads();
   }
-  const float inv = 1.f / (l_run + sink * expf(-m_run));  // the sink's score is 0: exp(0 - m) in the shifted sum
-  for (int c = threadIdx.x; c < dv; c += SA_THREADS) out[static_cast<long long>(t) * out_ld + h * dv + c] = from_f<T>(acc[c] * inv);
+  const float inv = 1.f / (l_run + sink * expf(-m_run));  // the constant sink's score is 0: exp(0 - m) in the shifted sum
+  for (int c = threadIdx.x; c < dv; c += SA_THREADS) out[static_cast<long long>(t) * out_ld + h * ex.out_head_stride + c] = from_f<T>(acc[c] * inv);
+}
+
+// One warp per (token, slot).  Slots 0 .. H - 1: the rotated part (the last dr entries) of query head h, rotated in place.  Slot H: the
+// low-rank row -- its first R entries RMS-normed with a weight, its last dr entries rotated -- goes to the token's row of the cache.
+template <typename T>
+__device__ __forceinline__ void rotate_half_row(const T* __restrict__ src, T* __restrict__ dst, int n, int rot, int pos, const double* __restrict__ freq,
+                                                int lane) {
+  const int half = rot >> 1;
+  for (int i = lane; i < half; i += 32) {
+    const float u = to_f(src[i]), v = to_f(src[i + half]);
+    double a = static_cast<double>(pos) * freq[i];
+    a -= 6.283185307179586476925 * rint(a * 0.15915494309189533576888);  // into [-pi, pi] before single precision takes over
+    float sn, cs;
+    sincosf(static_cast<float>(a), &sn, &cs);
+    dst[i] = from_f<T>(u * cs - v * sn);
+    dst[i + half] = from_f<T>(v * cs + u * sn);
+  }
+  if (dst != src)
+    for (int c = rot + lane; c < n; c += 32) dst[c] = src[c];
+}
+template <typename T>
+__global__ void latent_rotary_append_kernel(T* __restrict__ proj, long long ld, int q_col0, int kv_col0, const float* __restrict__ wkv,
+                                            const double* __restrict__ freq, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                            const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ cache, int row_w,
+                                            int n_tokens, int H, int d, int dr, int R, int rot, float eps) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= n_tokens * (H + 1)) return;
+  const int t = gw / (H + 1), slot = gw % (H + 1);
+  const int pos = tok_pos[t];
+  T* row = proj + static_cast<long long>(t) * ld;
+  if (slot < H) {
+    T* v = row + q_col0 + slot * (d + dr) + d;
+    rotate_half_row(v, v, dr, rot, pos, freq, lane);
+    return;
+  }
+  const T* low = row + kv_col0;
+  const long long blk = block_table[static_cast<size_t>(tok_seq[t]) * bt_stride + pos / block_size];
+  T* dst = cache + (blk * block_size + pos % block_size) * row_w;
+  float s = 0.f;
+  for (int c = lane; c < R; c += 32) { const float v = to_f(low[c]); s += v * v; }
+  s = warp_sum(s);
+  const float inv = 1.f / sqrtf(s / static_cast<float>(R) + eps);
+  for (int c = lane; c < R; c += 32) dst[c] = from_f<T>(to_f(low[c]) * inv * wkv[c]);
+  rotate_half_row(low + R, dst + R, dr, rot, pos, freq, lane);
+  for (int c = R + dr + lane; c < row_w; c += 32) dst[c] = from_f<T>(0.f);  // rows padded to a width the tensor-core kernels take
+}
+
+// One warp per (token, head slot): the H query heads, then the G key heads, then the G value heads of the token.  Every channel first passes
+// a short causal convolution over the sequence (bias added to every real row; rows before this step's come from the state, rows before the
+// sequence are zeros); query / key heads then get their RMS norm, value heads are mixed with another layer's values of the same token.
+template <typename T>
+__global__ void conv_head_norm_append_kernel(const T* __restrict__ proj, long long ld, int col0, const float* __restrict__ bias,
+                                             const float* __restrict__ conv_w, const float* __restrict__ wq, const float* __restrict__ wk,
+                                             const T* __restrict__ state, const int4* __restrict__ seq_desc, const int* __restrict__ tok_seq,
+                                             const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride, int block_size,
+                                             T* __restrict__ k_cache, long long k_block_stride, T* __restrict__ v_cache, long long v_block_stride,
+                                             T* __restrict__ q_out, long long q_ld, const T* __restrict__ v_other, const float* __restrict__ mix,
+                                             T* __restrict__ v_own, int n_tokens, int H, int G, int d, int dv, int taps, float eps, int q_row,
+                                             int k_row, int v_row) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int per_tok = H + 2 * G;
+  if (gw >= n_tokens * per_tok) return;
+  const int t = gw / per_tok, slot = gw % per_tok;
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  const int4 sd = seq_desc[seq];
+  const int i = t - sd.x;  // index among the sequence's new tokens
+  const int C = (H + G) * d + G * dv;  // convolved channels: q | k | v, as they lie in proj from col0 on and in the state rows
+  const bool is_q = slot < H, is_v = slot >= H + G;
+  const int head = is_q ? slot : (is_v ? slot - H - G : slot - H);
+  const int n = is_v ? dv : d;
+  const int ch0 = is_q ? head * d : (is_v ? (H + G) * d + head * dv : H * d + head * d);
+  const T* st = state ? state + static_cast<size_t>(sd.w) * (taps - 1) * C : nullptr;
+  long long cache_row = 0;
+  if (!is_q) cache_row = block_table[static_cast<size_t>(seq) * bt_stride + pos / block_size];
+  const int in_block = pos % block_size;
+  T* dst = is_q ? q_out + static_cast<long long>(t) * q_ld + head * q_row
+                : (is_v ? v_cache + cache_row * v_block_stride + (static_cast<long long>(in_block) * G + head) * v_row
+                        : k_cache + cache_row * k_block_stride + (static_cast<long long>(in_block) * G + head) * k_row);
+  const int width = is_q ? q_row : (is_v ? v_row : k_row);
+  // the head's channels: up to 8 per lane in registers, the rest recomputed (heads above 256 entries)
+  float ss = 0.f;
+  for (int pass = 0; pass < 2; ++pass) {
+    float inv = 1.f;
+    if (pass == 1) {
+      if (is_v) break;
+      ss = warp_sum(ss);
+      inv = 1.f / sqrtf(ss / static_cast<float>(n) + eps);
+    }
+    for (int c = lane; c < n; c += 32) {
+      const int ch = ch0 + c;
+      const float b = bias ? bias[ch] : 0.f;
+      float y = 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int ii = i - (taps - 1) + j;  // index among the new tokens of the row this tap reads
+        float u;
+        if (ii >= 0) u = to_f(proj[static_cast<long long>(sd.x + ii) * ld + col0 + ch]) + b;
+        else if (pos - i + ii >= 0) u = to_f(st[static_cast<size_t>(taps - 1 + ii) * C + ch]) + b;  // a row of an earlier step
+        else continue;  // before the sequence's start
+        y = fmaf(conv_w[static_cast<size_t>(ch) * taps + j], u, y);
+      }
+      if (is_v) {
+        const size_t vi = static_cast<size_t>(t) * G * dv + head * dv + c;
+        if (v_own) v_own[vi] = from_f<T>(y);
+        if (v_other) { const float lam = mix[0]; y = (1.f - lam) * y + lam * to_f(v_other[vi]); }
+        dst[c] = from_f<T>(y);
+      } else if (pass == 0) {
+        ss += y * y;
+      } else {
+        dst[c] = from_f<T>(y * inv * (is_q ? wq[c] : wk[c]));
+      }
+    }
+  }
+  for (int c = n + lane; c < width; c += 32) dst[c] = from_f<T>(0.f);  // padding: adds nothing to a score or an output
 }
 
 }  // namespace sinkattn
@@ -236,6 +365,24 @@ DSB_EXPORT int dsb200_head_norm_rotary_append(const void* proj, long long ld, in
   return DSB_OK;
 }
 
+static int launch_sink_attention(const void* q, long long q_ld, const void* k_cache, long long k_block_stride, const void* v_cache,
+                                 long long v_block_stride, const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
+                                 int block_size, void* out, long long out_ld, int n_tokens, int H, int G, int d, int dv, float scale, float cap,
+                                 float sink, const SinkExtras& ex, int dtype, cudaStream_t stream) {
+  const dim3 grid(n_tokens, H);
+  const size_t smem = static_cast<size_t>(d + dv) * sizeof(float);
+  if (dtype == 0)
+    sink_attention_kernel<bf16><<<grid, SA_THREADS, smem, stream>>>((const bf16*)q, q_ld, (const bf16*)k_cache, k_block_stride, (const bf16*)v_cache,
+                                                                    v_block_stride, tok_seq, tok_pos, block_table, bt_stride, block_size, (bf16*)out,
+                                                                    out_ld, H, G, d, dv, scale, cap, sink, ex);
+  else
+    sink_attention_kernel<float><<<grid, SA_THREADS, smem, stream>>>((const float*)q, q_ld, (const float*)k_cache, k_block_stride,
+                                                                     (const float*)v_cache, v_block_stride, tok_seq, tok_pos, block_table, bt_stride,
+                                                                     block_size, (float*)out, out_ld, H, G, d, dv, scale, cap, sink, ex);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
 // out[t, h dv + c] = sum_j p_j v_j[c] over the keys j <= pos(t) of the token's sequence, p_j = exp(s_j) / (sink + sum_j exp(s_j)),
 // s_j = scale q_h . k_j, soft-capped as cap tanh(s_j / cap) when cap > 0.  q [T, q_ld] (H heads of d); query head h reads key/value head
 // h / (H / G); out [T, out_ld] (H heads of dv).  CUDA cores, fp32 scores and accumulation, any sizes; dtype 0 = bf16, 1 = fp32.
@@ -246,16 +393,84 @@ DSB_EXPORT int dsb200_sink_attention(const void* q, long long q_ld, const void* 
   if (n_tokens == 0) return DSB_OK;
   DSB_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && d >= 1 && dv >= 1 && d + dv <= 8192 && sink >= 0.f, "sink_attention: heads %d / %d, head sizes %d / %d", H, G,
               d, dv);
-  const dim3 grid(n_tokens, H);
-  const size_t smem = static_cast<size_t>(d + dv) * sizeof(float);
+  const SinkExtras ex{nullptr, nullptr, nullptr, 0, d, dv, d, dv};
+  return launch_sink_attention(q, q_ld, k_cache, k_block_stride, v_cache, v_block_stride, tok_seq, tok_pos, block_table, bt_stride, block_size, out,
+                               out_ld, n_tokens, H, G, d, dv, scale, cap, sink, ex, dtype, stream);
+}
+
+// `sink_attention` with learned sinks, a distance term, a mask by parts and free strides:
+//   sink_logit [H] (or null): exp(sink_logit[h]) joins head h's denominator;   r1, r2 [H] (or both null): s_j -= r1[h] ln(1 + r2[h] (pos - j));
+//   part > 0: only the keys of the query's own part of `part` positions (counted from position 0 of the sequence) are visible;
+//   q[t * q_ld + h * q_head_stride + c], out[t * out_ld + h * out_head_stride + c]; a cached key / value head starts every k_row / v_row
+//   elements of its token's row (one plane may serve as keys and as values: pass it twice, with d and dv entries read from a head's start).
+DSB_EXPORT int dsb200_sink_attention_ex(const void* q, long long q_ld, long long q_head_stride, const void* k_cache, long long k_block_stride, int k_row,
+                                        const void* v_cache, long long v_block_stride, int v_row, const int* tok_seq, const int* tok_pos,
+                                        const int* block_table, int bt_stride, int block_size, void* out, long long out_ld, long long out_head_stride,
+                                        int n_tokens, int H, int G, int d, int dv, float scale, float cap, float sink, const float* sink_logit,
+                                        const float* r1, const float* r2, int part, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && d >= 1 && dv >= 1 && d + dv <= 8192 && sink >= 0.f && part >= 0 && k_row >= d && v_row >= dv &&
+                  (r1 == nullptr) == (r2 == nullptr),
+              "sink_attention: heads %d / %d, head sizes %d / %d, rows %d / %d, part %d", H, G, d, dv, k_row, v_row, part);
+  const SinkExtras ex{sink_logit, r1, r2, part, k_row, v_row, q_head_stride, out_head_stride};
+  return launch_sink_attention(q, q_ld, k_cache, k_block_stride, v_cache, v_block_stride, tok_seq, tok_pos, block_table, bt_stride, block_size, out,
+                               out_ld, n_tokens, H, G, d, dv, scale, cap, sink, ex, dtype, stream);
+}
+
+// Low-rank attention with one rotated key part shared by the heads.  proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds per token the H query heads
+// (d plain entries, then dr entries to rotate) from q_col0 and the low-rank row (R entries, then dr entries to rotate) from kv_col0.  The
+// query heads' rotated parts are rotated IN PLACE (first rot_dims of the dr entries; entry i pairs with entry i + rot_dims / 2; angle =
+// pos * freq[i], freq: rot_dims / 2 doubles on the device); the first R entries of the low-rank row are RMS-normed with wkv [R] and, with the
+// rotated last dr entries behind them, written to the token's row of cache [blocks, block_size, row_w] (zeros from R + dr on).
+DSB_EXPORT int dsb200_latent_rotary_append(void* proj, long long ld, int q_col0, int kv_col0, const float* wkv, const double* freq, const int* tok_seq,
+                                           const int* tok_pos, const int* block_table, int bt_stride, int block_size, void* cache, int row_w,
+                                           int n_tokens, int H, int d, int dr, int R, int rot_dims, float eps, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H >= 1 && d >= 0 && dr >= 0 && R >= 1 && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dr && (rot_dims == 0 || freq != nullptr) &&
+                  row_w >= R + dr && wkv != nullptr,
+              "latent_rotary_append: heads %d, head %d + %d, rank %d, rotated %d, row %d", H, d, dr, R, rot_dims, row_w);
+  const long long warps = static_cast<long long>(n_tokens) * (H + 1);
+  const int wpb = 8;
+  const int grid = static_cast<int>((warps + wpb - 1) / wpb);
   if (dtype == 0)
-    sink_attention_kernel<bf16><<<grid, SA_THREADS, smem, stream>>>((const bf16*)q, q_ld, (const bf16*)k_cache, k_block_stride, (const bf16*)v_cache,
-                                                                    v_block_stride, tok_seq, tok_pos, block_table, bt_stride, block_size, (bf16*)out,
-                                                                    out_ld, H, G, d, dv, scale, cap, sink);
+    latent_rotary_append_kernel<bf16><<<grid, wpb * 32, 0, stream>>>((bf16*)proj, ld, q_col0, kv_col0, wkv, freq, tok_seq, tok_pos, block_table, bt_stride,
+                                                                    block_size, (bf16*)cache, row_w, n_tokens, H, d, dr, R, rot_dims, eps);
   else
-    sink_attention_kernel<float><<<grid, SA_THREADS, smem, stream>>>((const float*)q, q_ld, (const float*)k_cache, k_block_stride,
-                                                                     (const float*)v_cache, v_block_stride, tok_seq, tok_pos, block_table, bt_stride,
-                                                                     block_size, (float*)out, out_ld, H, G, d, dv, scale, cap, sink);
+    latent_rotary_append_kernel<float><<<grid, wpb * 32, 0, stream>>>((float*)proj, ld, q_col0, kv_col0, wkv, freq, tok_seq, tok_pos, block_table,
+                                                                     bt_stride, block_size, (float*)cache, row_w, n_tokens, H, d, dr, R, rot_dims, eps);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Attention inputs behind a short causal convolution.  proj [T, ld] holds from col0 on the query heads [H d], the key heads [G d] and the value
+// heads [G dv] of every token; bias (fp32, that many entries, or null) is added to every row before the convolution with conv_w (fp32
+// [channels, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence's start).  state [slots, taps - 1, channels]: the last
+// rows of the sequence's earlier steps, WITHOUT the bias (update it afterwards with dsb200_conv_state_update).  Query / key heads: RMS norm over
+// d with wq / wk [d] shared by the heads -> q_out [T, q_ld] (head h at h * q_row) / the key plane.  Value heads: v_own (null, or [T, G dv])
+// receives the convolved values; with v_other ([T, G dv]) and mix (one float on the device) the cached value is (1 - mix) v + mix v_other.
+// Heads are padded with zeros to q_row / k_row / v_row entries.
+DSB_EXPORT int dsb200_conv_head_norm_append(const void* proj, long long ld, int col0, const float* bias, const float* conv_w, const float* wq,
+                                            const float* wk, const void* state, const int* seq_desc, const int* tok_seq, const int* tok_pos,
+                                            const int* block_table, int bt_stride, int block_size, void* k_cache, long long k_block_stride,
+                                            void* v_cache, long long v_block_stride, void* q_out, long long q_ld, const void* v_other,
+                                            const float* mix, void* v_own, int n_tokens, int H, int G, int d, int dv, int taps, float eps, int q_row,
+                                            int k_row, int v_row, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H >= 1 && G >= 1 && d >= 1 && dv >= 1 && taps >= 1 && (taps == 1 || state != nullptr) && conv_w != nullptr && wq != nullptr &&
+                  wk != nullptr && (v_other == nullptr || mix != nullptr),
+              "conv_head_norm_append: heads %d / %d, head sizes %d / %d, taps %d", H, G, d, dv, taps);
+  DSB_REQUIRE(q_row >= d && k_row >= d && v_row >= dv, "conv_head_norm_append: row widths %d / %d / %d below the head sizes %d / %d", q_row, k_row, v_row, d, dv);
+  const long long warps = static_cast<long long>(n_tokens) * (H + 2 * G);
+  const int wpb = 8;
+  const int grid = static_cast<int>((warps + wpb - 1) / wpb);
+#define LAUNCH(T)                                                                                                                                     \
+  conv_head_norm_append_kernel<T><<<grid, wpb * 32, 0, stream>>>((const T*)proj, ld, col0, bias, conv_w, wq, wk, (const T*)state, (const int4*)seq_desc, tok_seq, \
+                                                                 tok_pos, block_table, bt_stride, block_size, (T*)k_cache, k_block_stride, (T*)v_cache,         \
+                                                                 v_block_stride, (T*)q_out, q_ld, (const T*)v_other, mix, (T*)v_own, n_tokens, H, G, d, dv,     \
+                                                                 taps, eps, q_row, k_row, v_row)
+  if (dtype == 0) LAUNCH(bf16);
+  else LAUNCH(float);
+#undef LAUNCH
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

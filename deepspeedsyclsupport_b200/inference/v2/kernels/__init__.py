@@ -715,3 +715,132 @@ def paged_flash_sink(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, scal
                                                       float(scale), float(softcap), float(sink), max_atoms, n_splits, native.ptr(scratch), int(decode),
                                                       native.stream_ptr()), 2 + (n_splits > 1))
     return out
+
+
+# ---- blocks whose norm sits behind the residual sum, xIELU, scalar head gates (csrc/ragged/latent_ops.cu); attention inputs behind a short
+# convolution, low-rank attention with a shared rotated key part, attention with learned sinks / a distance term / a mask by parts
+# (csrc/ragged/sink_attention_ops.cu); the minimal gated recurrence (csrc/ragged/recurrent_ops.cu)
+native.register_sigs({
+    "dsb200_post_sum_norm": "pp i ppp p i l i ff p",
+    "dsb200_xielu": "p l p l i p i p",
+    "dsb200_gate_heads_scalar": "pp l p l iii i p",
+    "dsb200_mingru_scratch_floats": "iii",
+    "dsb200_mingru_scan": "p l iii pp pp p p l iii i p i p",
+    "dsb200_sink_attention_ex": "p l l p l i p l i ppp ii p l l iiiii fff ppp i i p",
+    "dsb200_latent_rotary_append": "p l ii pp ppp ii p i iiiii i f i p",
+    "dsb200_conv_head_norm_append": "p l i pppp p pppp ii p l p l p l p p p iiiiii f iii i p",
+}, restype_long=("dsb200_mingru_scratch_floats", ))
+
+
+def post_sum_norm(x, y=None, w=None, alpha=1.0, eps=1e-6, y32=None, bias=None, out_dtype=torch.bfloat16):
+    """On the fp32 residual x [T, dim], in place: x <- rms_norm(alpha x + y + y32 + bias) * w, eps inside the root (y in an activation dtype,
+    y32 fp32, bias fp32 [dim]; each optional).  Returns the new stream in `out_dtype` (x itself for fp32)."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.is_cuda and w is not None and w.dtype == torch.float32
+    if y is not None:
+        assert y.shape == x.shape
+        y = y if y.is_contiguous() else y.contiguous()  # a GEMM output whose rows were padded to the TMA stride (odd widths only)
+    assert y32 is None or (y32.shape == x.shape and y32.dtype == torch.float32 and y32.is_contiguous())
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == x.shape[1])
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out_dtype != torch.float32 else None
+    native.check(native.lib().dsb200_post_sum_norm(native.ptr(x), native.ptr(y), _dt(y) if y is not None else 0, native.ptr(y32), native.ptr(bias),
+                                                   native.ptr(w), native.ptr(out), _DT[out_dtype], x.shape[0], x.shape[1], float(alpha), float(eps),
+                                                   native.stream_ptr()))
+    return out if out is not None else x
+
+
+def xielu_coefficients(p, q):
+    """(softplus(p), 1/2 + softplus(q)) as the fp32 pair the kernel reads, formed in double precision."""
+    return torch.tensor([math.log1p(math.exp(float(p))), 0.5 + math.log1p(math.exp(float(q)))], dtype=torch.float32)
+
+
+def xielu(u, coef):
+    """u [rows, F] (unit column stride) -> [rows, F]: z > 0: coef[0] z^2 + z / 2; z <= 0: coef[1] (exp(z) - 1 - z) + z / 2; coef fp32 [2] on the device."""
+    assert u.stride(1) == 1 and coef.dtype == torch.float32 and coef.numel() == 2 and coef.is_cuda
+    out = torch.empty(u.shape, dtype=u.dtype, device=u.device)
+    native.check(native.lib().dsb200_xielu(native.ptr(u), u.stride(0), native.ptr(out), u.shape[0], u.shape[1], native.ptr(coef), _dt(u),
+                                           native.stream_ptr()))
+    return out
+
+
+def gate_heads_scalar(a, gate, out=None):
+    """a [H, T, dv] (contiguous result of a per-head batched GEMM), gate [T, >= H] (unit column stride): one number per token and head ->
+    [T, H * dv]: the heads side by side, each times the sigmoid of its number."""
+    H, T, dv = a.shape
+    assert a.is_contiguous() and gate.shape[0] == T and gate.stride(1) == 1 and gate.dtype == a.dtype
+    if out is None:
+        out = torch.empty(T, H * dv, dtype=a.dtype, device=a.device)
+    assert out.stride(1) == 1 and out.dtype == a.dtype
+    native.check(native.lib().dsb200_gate_heads_scalar(native.ptr(a), native.ptr(gate), gate.stride(0), native.ptr(out), out.stride(0), T, H, dv, _dt(a),
+                                                       native.stream_ptr()))
+    return out
+
+
+def mingru_scan(proj, z_col0, x_col0, g_col0, z_bias, x_bias, tok_seq, seq_desc, n_seqs, state, out, W, pieces=None):
+    """Minimal gated recurrence over every sequence's new tokens: z = sigmoid(proj[:, z_col0:] + z_bias), u = proj[:, x_col0:] + x_bias,
+    S <- (1 - z) S + z (u + 1/2 if u >= 0 else sigmoid(u)), out = S silu(proj[:, g_col0:]); state fp32 [slots, W] (a sequence at position 0
+    starts from zero).  `pieces`: cut the batch's rows into pieces that are walked side by side (default: when there are more rows than
+    sequences x 64); else one thread per (sequence, channel) walks its tokens in order."""
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and out.stride(1) == 1 and out.dtype == proj.dtype and state.dtype == torch.float32 and state.shape[1] == W
+    assert z_bias.dtype == torch.float32 and x_bias.dtype == torch.float32 and z_bias.numel() == W == x_bias.numel()
+    if pieces is None:
+        pieces = T > 64 * n_seqs
+    scratch = None
+    if pieces:
+        scratch = torch.empty(native.lib().dsb200_mingru_scratch_floats(T, n_seqs, W), dtype=torch.float32, device=proj.device)
+    native.check(native.lib().dsb200_mingru_scan(native.ptr(proj), proj.stride(0), z_col0, x_col0, g_col0, native.ptr(z_bias), native.ptr(x_bias),
+                                                 native.ptr(tok_seq), native.ptr(seq_desc), native.ptr(state), native.ptr(out), out.stride(0), T, n_seqs,
+                                                 W, int(bool(pieces)), native.ptr(scratch), _dt(proj), native.stream_ptr()), 3 if pieces else 1)
+    return out
+
+
+def sink_attention_ex(q, q_head_stride, k_plane, k_row, v_plane, v_row, tok_seq, tok_pos, block_table, block_size, out, out_head_stride, H, G, d, dv,
+                      scale, softcap=0.0, sink=0.0, sink_logit=None, r1=None, r2=None, part=0):
+    """`sink_attention` with learned sinks (sink_logit fp32 [H]: exp of it joins the head's denominator), a distance term (r1, r2 fp32 [H]: the
+    score of key j loses r1 ln(1 + r2 (pos - j))), a mask by parts (`part` > 0: a query sees only the keys of its own part of that many
+    positions, counted from the sequence's start) and free strides: q / out are addressed [t * stride(0) + h * head_stride + c], a cached
+    key / value head starts every k_row / v_row elements of its token's row."""
+    T = q.shape[0]
+    (kc, ks), (vc, vs) = k_plane, v_plane
+    assert q.dtype == kc.dtype == vc.dtype == out.dtype
+    for p in (sink_logit, r1, r2):
+        assert p is None or (p.dtype == torch.float32 and p.numel() == H and p.is_cuda)
+    native.check(native.lib().dsb200_sink_attention_ex(native.ptr(q), q.stride(0), int(q_head_stride), native.ptr(kc), ks, int(k_row), native.ptr(vc), vs,
+                                                       int(v_row), native.ptr(tok_seq), native.ptr(tok_pos), native.ptr(block_table),
+                                                       block_table.stride(0), int(block_size), native.ptr(out), out.stride(0), int(out_head_stride), T,
+                                                       H, G, d, dv, float(scale), float(softcap), float(sink), native.ptr(sink_logit), native.ptr(r1),
+                                                       native.ptr(r2), int(part), _dt(q), native.stream_ptr()))
+    return out
+
+
+def latent_rotary_append(proj, q_col0, kv_col0, wkv, freq, tok_seq, tok_pos, block_table, cache, H, d, dr, R, rot_dims, eps):
+    """proj [T, N] holds the H query heads (d plain + dr rotated entries each) from q_col0 and the low-rank row (R + dr entries) from kv_col0.
+    The rotated parts of the query heads are rotated in place (rotate-half pairs over the first rot_dims of the dr entries, angle pos * freq[i]);
+    the RMS-normed (weight wkv) first R entries of the low-rank row and its rotated last dr entries go to the token's row of
+    cache [blocks, block_size, row >= R + dr] (zeros behind)."""
+    assert proj.stride(1) == 1 and cache.is_contiguous() and cache.dim() == 3 and cache.dtype == proj.dtype
+    native.check(native.lib().dsb200_latent_rotary_append(native.ptr(proj), proj.stride(0), q_col0, kv_col0, native.ptr(wkv), native.ptr(freq),
+                                                          native.ptr(tok_seq), native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0),
+                                                          cache.shape[1], native.ptr(cache), cache.shape[2], proj.shape[0], H, d, dr, R, int(rot_dims),
+                                                          float(eps), _dt(proj), native.stream_ptr()))
+
+
+def conv_head_norm_append(proj, col0, bias, conv_w, wq, wk, state, seq_desc, tok_seq, tok_pos, block_table, block_size, k_plane, v_plane, q_out,
+                          H, G, d, dv, taps, eps, v_other=None, mix=None, v_own=None, row=None):
+    """Query heads [H d], key heads [G d] and value heads [G dv] lie side by side in proj from column col0.  Every channel gets its bias
+    (fp32, or None) and a short causal convolution (conv_w fp32 [channels, taps]; rows before this step's come from state
+    [slots, taps - 1, channels], rows before the sequence are zeros); query / key heads are RMS-normed with wq / wk [d] (shared by the heads);
+    queries -> q_out, keys / values -> their planes.  v_own ([T, G dv]): receives the convolved values; v_other + mix (fp32 [1]): the cached
+    value is (1 - mix) v + mix v_other.  `row`: heads are padded with zeros to this width."""
+    (kc, ks), (vc, vs) = k_plane, v_plane
+    assert proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.dtype == proj.dtype == kc.dtype == vc.dtype
+    for v in (v_other, v_own):
+        assert v is None or (v.is_contiguous() and v.dtype == proj.dtype and v.shape == (proj.shape[0], G * dv))
+    assert state is None or (state.dtype == proj.dtype and state.is_contiguous())
+    native.check(native.lib().dsb200_conv_head_norm_append(native.ptr(proj), proj.stride(0), col0, native.ptr(bias), native.ptr(conv_w), native.ptr(wq),
+                                                           native.ptr(wk), native.ptr(state), native.ptr(seq_desc), native.ptr(tok_seq),
+                                                           native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0), int(block_size),
+                                                           native.ptr(kc), ks, native.ptr(vc), vs, native.ptr(q_out), q_out.stride(0),
+                                                           native.ptr(v_other), native.ptr(mix), native.ptr(v_own), proj.shape[0], H, G, d, dv, int(taps),
+                                                           float(eps), int(row or d), int(row or d), int(row or dv), _dt(proj), native.stream_ptr()))
+    return q_out

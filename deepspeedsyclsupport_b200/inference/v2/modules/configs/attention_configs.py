@@ -178,3 +178,74 @@ class DSSinkAttentionConfig(DSModuleConfig):
     @property
     def group_size(self) -> int:
         return self.n_heads_q // self.n_heads_kv
+
+
+class DSRotaryLatentAttentionConfig(DSModuleConfig):
+    """Attention whose keys and values are per-head up-projections of one cached, RMS-normed low-rank latent per token, with a rotated part
+    beside it: a query head has `qk_dim` plain and `rot_dim` rotated entries; every token adds ONE rotated key part of `rot_dim` entries that
+    all heads share, cached beside the latent.  score = scale (q_plain . W_uk c + q_rot . k_rot); rotate-half pairs over the first `rotate_dim`
+    of the rot_dim entries; causal softmax, optionally with a learned sink per head (exp(sink_h) joins the denominator) and a sigmoid gate
+    per token and head on the head's output."""
+    n_heads: int
+    qk_dim: int  # plain (unrotated) query / key entries per head
+    rot_dim: int  # rotated entries per query head = size of the shared key part
+    v_dim: int
+    kv_rank: int
+    scale: float
+    rotate_dim: int  # entries of the rot_dim part that are rotated (pairs (i, i + rotate_dim / 2)); the rest pass unchanged
+    theta_base: float = 10_000.0
+    learned_sink: bool = False
+    head_gate: bool = False
+    eps: float = 1e-6  # of the latent's norm
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16
+
+    @model_validator(mode="after")
+    def _consistent(self):
+        for k in ("n_heads", "v_dim", "kv_rank"):
+            if getattr(self, k) <= 0:
+                raise ValueError(f"{k} must be positive")
+        if self.qk_dim < 0 or self.rot_dim < 0 or self.qk_dim + self.rot_dim <= 0:
+            raise ValueError("a query head needs at least one entry")
+        if not (0 <= self.rotate_dim <= self.rot_dim and self.rotate_dim % 2 == 0):
+            raise ValueError(f"rotate_dim must be even and at most rot_dim ({self.rot_dim}), got {self.rotate_dim}")
+        if self.kv_rank + self.rot_dim > 4096:
+            raise ValueError("the attention kernels hold a cached row of at most 4096 values")
+        return self
+
+
+class DSConvSinkAttentionConfig(DSModuleConfig):
+    """Attention whose query, key and value projections (with biases) pass a short causal convolution over time, then per-head RMS norms of
+    queries and keys (one weight of head size shared by the heads); no rotation.  score = scale q . k - r1_h ln(1 + r2_h (i - j)) when
+    `distance_bias`; a query at position i sees the keys j <= i of its own part, floor(i / part_size) = floor(j / part_size) (0: all);
+    `learned_sink`: exp(sink_h) joins the softmax denominator.  `value_mix`: "source" = the layer's convolved values are handed to later
+    layers; "mix" = the cached value is (1 - m) v + m v_source with the source layer's values of the same token; "none"."""
+    n_heads_q: int
+    n_heads_kv: int
+    head_size: int
+    value_size: int
+    conv_taps: int  # the last taps - 1 projected rows of a sequence are state
+    scale: float
+    part_size: int = 0
+    distance_bias: bool = False
+    learned_sink: bool = False
+    value_mix: str = "none"
+    eps: float = 1e-6
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16
+
+    @model_validator(mode="after")
+    def _consistent(self):
+        if self.n_heads_q <= 0 or self.n_heads_kv <= 0 or self.n_heads_q % self.n_heads_kv != 0:
+            raise ValueError(f"n_heads_q ({self.n_heads_q}) must be a positive multiple of n_heads_kv ({self.n_heads_kv})")
+        if self.head_size <= 0 or self.value_size <= 0 or self.conv_taps < 1 or self.part_size < 0:
+            raise ValueError("head sizes and conv_taps must be positive, part_size cannot be negative")
+        if self.value_mix not in ("none", "source", "mix"):
+            raise ValueError(f"value_mix must be none, source or mix, got {self.value_mix}")
+        return self
+
+    @property
+    def group_size(self) -> int:
+        return self.n_heads_q // self.n_heads_kv

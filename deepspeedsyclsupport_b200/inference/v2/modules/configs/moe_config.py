@@ -29,3 +29,5 @@ class DSMoEConfig(DSModuleConfig):
     # identity experts: the router has n_experts + n_identity_experts outputs; the last n_identity_experts of them have no weights and
     # return their input (times the routing weight)
     n_identity_experts: int = 0
+    # the weighted sum of the experts' outputs leaves in fp32 (it joins an fp32 residual stream) whatever the activation dtype
+    fp32_combine: bool = False

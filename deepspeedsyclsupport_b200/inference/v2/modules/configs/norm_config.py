@@ -26,6 +26,10 @@ class DSNormConfig(DSModuleConfig):
     # own root mean square, before the weight is applied.
     shared_input: bool = False
     groups: int = 1
+    # "post sum" blocks: the norm sits BEHIND the residual sum and its result IS the new stream: x <- norm(stream_mult * x + sublayer(x)) * w.
+    # The sublayers read the stream itself; the stream is kept in fp32 and handed on in the activation dtype as well.
+    post_sum: bool = False
+    stream_mult: float = 1.0
 
     @field_validator("channels")
     @classmethod

@@ -46,3 +46,13 @@ class DSTiedGateConfig(DSModuleConfig):
     max_sequences: int
     input_dtype: DtypeEnum = DtypeEnum.bf16
     output_dtype: DtypeEnum = DtypeEnum.bf16
+
+
+class DSMinGRUConfig(DSModuleConfig):
+    """Minimal gated recurrence with one number of state per channel; the gates read only the current token: z = sigmoid(W_z h + b_z),
+    u = W_x h + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u) below, S <- (1 - z) S + z c, output S silu(W_g h) (before the output
+    projection).  The state is fp32 and starts at zero."""
+    width: int
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16

@@ -15,4 +15,5 @@ class DSUnembedConfig(DSModuleConfig):
     norm_weight_offset: float = 0.0  # the final norm multiplies by (weight + offset): 1.0 for zero-centred weights (applied as 1 + w)
     logit_softcap: float = 0.0  # > 0: logits <- cap * tanh(logits / cap)
     residual_fp32: bool = False  # the hidden states arrive as the fp32 residual stream; logits leave in fp32
+    logit_scale: float = 1.0  # the logits are multiplied by this (folded into the final norm's weight: `transform_norm_param`)
     norm_groups: int = 1  # with residual_fp32: the final RMS norm works on this many equal consecutive parts of the row, each on its own

@@ -4,8 +4,9 @@ quantisation mode selects the fp8 tensor-core linear; everything else currently 
 from ..config_v2 import RaggedInferenceEngineConfig
 from ..inference_utils import ActivationType, NormTypeEnum
 from . import implementations  # noqa: F401  (registers the implementations)
-from .configs import (DSDeltaRuleConfig, DSEmbeddingsConfig, DSLatentAttentionConfig, DSLinearConfig, DSMatrixMemoryConfig, DSMoEConfig, DSNormConfig,
-                      DSSelfAttentionConfig, DSSinkAttentionConfig, DSTiedGateConfig, DSUnembedConfig, DSWindowedAttentionConfig)
+from .configs import (DSConvSinkAttentionConfig, DSDeltaRuleConfig, DSEmbeddingsConfig, DSLatentAttentionConfig, DSLinearConfig, DSMatrixMemoryConfig,
+                      DSMinGRUConfig, DSMoEConfig, DSNormConfig, DSRotaryLatentAttentionConfig, DSSelfAttentionConfig, DSSinkAttentionConfig,
+                      DSTiedGateConfig, DSUnembedConfig, DSWindowedAttentionConfig)
 from .interfaces import (DSEmbeddingBase, DSEmbeddingRegistry, DSLinearBase, DSLinearRegistry, DSMoEBase, DSMoERegistry, DSPostNormBase,
                          DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry, DSRecurrentMixerBase, DSRecurrentRegistry, DSSelfAttentionBase,
                          DSSelfAttentionRegistry, DSUnembedBase, DSUnembedRegistry)
@@ -20,6 +21,10 @@ def _quant_mode(engine_config) -> str:
 def instantiate_attention(attention_config, engine_config: RaggedInferenceEngineConfig = None) -> DSSelfAttentionBase:
     if isinstance(attention_config, DSLatentAttentionConfig):  # keys / values are up-projections of a cached latent
         return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="latent_blocked_attention", config=attention_config))
+    if isinstance(attention_config, DSRotaryLatentAttentionConfig):  # a cached latent with one rotated key part beside it, learned sinks
+        return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="rotary_latent_attention", config=attention_config))
+    if isinstance(attention_config, DSConvSinkAttentionConfig):  # convolved q / k / v, distance term, mask by parts, learned sinks, value mixing
+        return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="conv_sink_attention", config=attention_config))
     if isinstance(attention_config, DSWindowedAttentionConfig):  # convolved q / k, values = keys, sliding window that keeps the first tokens
         return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="windowed_conv_attention", config=attention_config))
     if isinstance(attention_config, DSSinkAttentionConfig):  # per-head q / k / v norms, soft-capped scores, a sink in the softmax
@@ -29,7 +34,8 @@ def instantiate_attention(attention_config, engine_config: RaggedInferenceEngine
 
 def instantiate_recurrent(mixer_config, engine_config: RaggedInferenceEngineConfig = None) -> DSRecurrentMixerBase:
     """Token mixers with a fixed-size state per sequence; the config class names the recurrence."""
-    name = {DSMatrixMemoryConfig: "matrix_memory", DSDeltaRuleConfig: "channel_delta_rule", DSTiedGateConfig: "tied_gate_linear"}[type(mixer_config)]
+    name = {DSMatrixMemoryConfig: "matrix_memory", DSDeltaRuleConfig: "channel_delta_rule", DSTiedGateConfig: "tied_gate_linear",
+            DSMinGRUConfig: "min_gru"}[type(mixer_config)]
     return DSRecurrentRegistry.instantiate_config(ConfigBundle(name=name, config=mixer_config))
 
 
@@ -52,14 +58,15 @@ def instantiate_linear(linear_config: DSLinearConfig, engine_config: RaggedInfer
 
 def instantiate_moe(moe_config: DSMoEConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSMoEBase:
     if (moe_config.n_groups > 1 or moe_config.use_correction or ActivationType(moe_config.activation) == ActivationType.ClampedSwiGLU or
-            moe_config.score_function != "softmax" or moe_config.scale_input or moe_config.n_identity_experts > 0):
+            moe_config.score_function != "softmax" or moe_config.scale_input or moe_config.n_identity_experts > 0 or moe_config.fp32_combine):
         return DSMoERegistry.instantiate_config(ConfigBundle(name="grouped_topk_moe", config=moe_config))
     bundle = ConfigBundle(name="cutlass_multi_gemm_moe", config=moe_config, implementation_config={"weight_dtype": moe_config.input_dtype})
     return DSMoERegistry.instantiate_config(bundle)
 
 
 def instantiate_post_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSPostNormBase:
-    return DSPostNormRegistry.instantiate_config(ConfigBundle(name="cuda_post_ln", config=norm_config))
+    name = "cuda_post_sum_rms" if (NormTypeEnum(norm_config.type) == NormTypeEnum.RMSNorm and norm_config.post_sum) else "cuda_post_ln"
+    return DSPostNormRegistry.instantiate_config(ConfigBundle(name=name, config=norm_config))
 
 
 def instantiate_pre_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSPreNormBase:

@@ -31,6 +31,10 @@ class DSRaggedUnembed(DSUnembedBase):
     def output(self) -> torch.Tensor:
         return self._output
 
+    def transform_norm_param(self, param: torch.Tensor) -> torch.Tensor:
+        """Weight of the final norm in fp32, times `logit_scale`: scale * (W (n * w)) = W (n * (scale w)), so the constant costs no pass."""
+        return param.to(torch.float32) * self._config.logit_scale if self._config.logit_scale != 1.0 else param.to(torch.float32)
+
     def forward(self, hidden_states: torch.Tensor, vocab_embedding: torch.Tensor, ragged_metadata, bias: Optional[torch.Tensor] = None,
                 gamma: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
                 residual: Optional[torch.Tensor] = None, pending=None) -> torch.Tensor:
