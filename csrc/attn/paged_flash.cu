@@ -76,6 +76,12 @@ struct Params {
   // and cap_in = 2 log2(e) scale / cap (raw = q . k); cap_l2 = 0: no cap.  Not combined with ALiBi.
   float cap_l2, cap_in;
   float sink;          // added to the softmax denominator in units of exp(0): 1 = one more, valueless entry of score 0; 0 = plain softmax
+  const float* sink_logit;  // optional [hq] learned sinks: exp(sink_logit[head]) joins the head's denominator; nullptr = none
+  // distance term: the score of key j for the query at position i loses r1[head] ln(1 + r2[head] (i - j)), formed in the exp2 domain as
+  // r1 log2(1 + r2 (i - j)) (one MUFU lg2 per score); nullptr = none.  Not combined with ALiBi or the soft cap.
+  const float* r1;
+  const float* r2;
+  int part;            // > 0: a query at position i sees only the keys j <= i with j / part == i / part (parts counted from position 0)
   long long* trace;  // diagnostics only (DSB200_PF_TRACE=1): clock64 stamps of the first CTA with >= 8 pages, [page][8 events]
 };
 // events: 0 K landed (MMA thread)  1 P ready seen by the MMA thread  2 S ready seen by softmax  3 P published  4 partial O read
@@ -171,7 +177,7 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int n_pages = (pos0 + nt + BN - 1) / BN;
   // pages that can hold a visible key: with a window, the pages of the kept first keys and the pages from the window's start (of the
   // atom's first token) on; list index j stands for page page_of(j)
-  const int win_pg = p.window > 0 ? max(0, pos0 + 1 - p.window) / BN : 0;
+  const int win_pg = p.window > 0 ? max(0, pos0 + 1 - p.window) / BN : (p.part > 0 ? ((pos0 / p.part) * p.part) / BN : 0);
   const int keep_pg = min((p.keep + BN - 1) / BN, win_pg);
   const int n_list = keep_pg + (n_pages - win_pg);
   auto page_of = [&](int j) { return j < keep_pg ? j : win_pg + (j - keep_pg); };
@@ -290,7 +296,8 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // keys [0, limit) are visible.  Dead rows (past the atom) see everything: their operands are finite (TMA zero fill /
       // other tokens' rows, zero-initialised cache) and nothing of theirs is stored
       const int limit = live ? pos0 + ti + 1 : 0x3fffffff;
-      const int first = (live && p.window > 0) ? max(0, pos0 + ti + 1 - p.window) : 0;  // first visible key (local attention)
+      // first visible key (local attention, or the start of the query's own part)
+      const int first = !live ? 0 : (p.window > 0 ? max(0, pos0 + ti + 1 - p.window) : (p.part > 0 ? ((pos0 + ti) / p.part) * p.part : 0));
       constexpr int DQ = D / 4;
       // m_run is the reference maximum P and O are expressed in.  It follows the true running maximum lazily: only when that
       // has grown by more than 2^8 is O (in TMEM, accumulated by the tensor core) read, rescaled and written back.  Reading
@@ -301,7 +308,9 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const bool has_alibi = p.alibi != nullptr;
       const float slope_l2 = (has_alibi && live) ? p.alibi[kvh * p.group + g] * 1.4426950408889634f : 0.f;
       const bool has_cap = p.cap_l2 > 0.f;  // capped scores are formed in the exp2 domain too
-      const float sl2 = (has_alibi || has_cap) ? 1.f : p.scale_log2;
+      const bool has_dist = p.r1 != nullptr;  // so is the distance term
+      const float r1h = (has_dist && live) ? p.r1[kvh * p.group + g] : 0.f, r2h = (has_dist && live) ? p.r2[kvh * p.group + g] : 0.f;
+      const float sl2 = (has_alibi || has_cap || has_dist) ? 1.f : p.scale_log2;
       __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(smem + SMEM::X_OFF);  // [part][row]
       const uint32_t bar_a = 1 + q4, bar_b = 5 + q4;  // the 4 warps (128 threads) that share the rows of this quarter
       const uint32_t o_addr = TM_O + part * DQ + lane_off;
@@ -355,6 +364,12 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const float key0f = static_cast<float>(key0);
 #pragma unroll
           for (int i = 0; i < 32; ++i) sv[i] = __float_as_uint(fmaf(__uint_as_float(sv[i]), p.scale_log2, slope_l2 * (key0f + i)));
+        }
+        if (has_dist) {  // behind the mask: a hidden key stays at -inf; its (negative) distance is clamped so that the logarithm stays finite
+          const float d0 = static_cast<float>(pos0 + ti - key0);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            sv[i] = __float_as_uint(fmaf(__uint_as_float(sv[i]), p.scale_log2, -r1h * __log2f(fmaf(r2h, fmaxf(d0 - i, 0.f), 1.f))));
         }
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -431,6 +446,7 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int t = t0 + ti, head = kvh * p.group + g;
         if (!partial) {
           if (p.sink > 0.f) l_run += p.sink * exp2f(m_run == -INFINITY ? 0.f : -m_run);  // the sink's score is 0 (splits: added by the merge)
+          if (p.sink_logit != nullptr) l_run += exp2f(p.sink_logit[head] * 1.4426950408889634f - (m_run == -INFINITY ? 0.f : m_run));
           const float inv_l = p.out_scale / l_run;
           __nv_bfloat16* dst = p.out + static_cast<size_t>(t) * p.out_ld + head * D + part * DQ;
 #pragma unroll
@@ -574,7 +590,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int n_pages = (pos0 + nt + BN - 1) / BN;
   // pages that can hold a visible key: with a window, the pages of the kept first keys and the pages from the window's start (of the
   // atom's first token) on; list index j stands for page page_of(j)
-  const int win_pg = p.window > 0 ? max(0, pos0 + 1 - p.window) / BN : 0;
+  const int win_pg = p.window > 0 ? max(0, pos0 + 1 - p.window) / BN : (p.part > 0 ? ((pos0 / p.part) * p.part) / BN : 0);
   const int keep_pg = min((p.keep + BN - 1) / BN, win_pg);
   const int n_list = keep_pg + (n_pages - win_pg);
   auto page_of = [&](int j) { return j < keep_pg ? j : win_pg + (j - keep_pg); };
@@ -694,16 +710,20 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float m_run[CPT], l_part[CPT];  // reference maximum per column (uniform over the part), this key-lane's share of the sums
       int limit[CPT], first[CPT];     // keys [first, limit) are visible to column c
       float slope_l2[CPT];            // ALiBi slope of the column's head, exp2 domain (0 without ALiBi)
+      float r1h[CPT], r2h[CPT];       // distance term of the column's head (0 without one)
       const bool has_alibi = p.alibi != nullptr;
       const bool has_cap = p.cap_l2 > 0.f;
-      const float sl2 = (has_alibi || has_cap) ? 1.f : p.scale_log2;
+      const bool has_dist = p.r1 != nullptr;
+      const float sl2 = (has_alibi || has_cap || has_dist) ? 1.f : p.scale_log2;
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
         m_run[i] = -INFINITY;
         l_part[i] = 0.f;
         limit[i] = c0 + i < nq ? pos0 + (c0 + i) / p.group + 1 : 0x3fffffff;
-        first[i] = (c0 + i < nq && p.window > 0) ? max(0, limit[i] - p.window) : 0;
+        first[i] = c0 + i >= nq ? 0 : (p.window > 0 ? max(0, limit[i] - p.window) : (p.part > 0 ? ((limit[i] - 1) / p.part) * p.part : 0));
         slope_l2[i] = (has_alibi && c0 + i < nq) ? p.alibi[kvh * p.group + (c0 + i) % p.group] * 1.4426950408889634f : 0.f;
+        r1h[i] = (has_dist && c0 + i < nq) ? p.r1[kvh * p.group + (c0 + i) % p.group] : 0.f;
+        r2h[i] = (has_dist && c0 + i < nq) ? p.r2[kvh * p.group + (c0 + i) % p.group] : 0.f;
       }
       const uint32_t s_addr0 = tmem_base + c0 + lane_off, o_addr = tmem_base + 32 + c0 + lane_off;
       for (int j = 0; j < n_blocks; ++j) {
@@ -723,6 +743,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float raw = has_cap ? soft_cap_l2(__uint_as_float(sv[i]), p.cap_in, p.cap_l2) : __uint_as_float(sv[i]);
           s[i] = (key >= limit[i] || (key < first[i] && key >= p.keep)) ? -INFINITY : raw;
           if (has_alibi) s[i] = fmaf(s[i], p.scale_log2, slope_l2[i] * static_cast<float>(key));
+          if (has_dist) s[i] = fmaf(s[i], p.scale_log2, -r1h[i] * __log2f(fmaf(r2h[i], fmaxf(static_cast<float>(limit[i] - 1 - key), 0.f), 1.f)));
           const uint32_t bits = __float_as_uint(s[i]);
           const uint32_t r = __reduce_max_sync(0xffffffffu, bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
           wm[i] = __uint_as_float(r ^ ((r >> 31) ? 0x80000000u : 0xffffffffu));
@@ -805,6 +826,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const int t = t0 + c / p.group, head = kvh * p.group + c % p.group;
           if (!partial) {
             if (p.sink > 0.f) l += p.sink * exp2f(m_run[i] == -INFINITY ? 0.f : -m_run[i]);  // the sink's score is 0 (splits: added by the merge)
+            if (p.sink_logit != nullptr) l += exp2f(p.sink_logit[head] * 1.4426950408889634f - (m_run[i] == -INFINITY ? 0.f : m_run[i]));
             p.out[static_cast<size_t>(t) * p.out_ld + head * D + row] = __float2bfloat16_rn(__uint_as_float(ov[i]) / l * p.out_scale);
           } else {
             const size_t slot = (static_cast<size_t>(t) * p.hq + head) * p.n_splits + split;
@@ -834,10 +856,19 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
+// what only some callers set: learned sinks, the distance term, the mask by parts (see Params)
+struct MaskExtras {
+  const float* sink_logit = nullptr;
+  const float* r1 = nullptr;
+  const float* r2 = nullptr;
+  int part = 0;
+};
+
 // out[t][h][:] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s ; one warp per (token, head)
 template <int D>
 __global__ void combine_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                                      int rows, int n_splits, int hq, long long out_ld, float out_scale, float sink) {
+                                      int rows, int n_splits, int hq, long long out_ld, float out_scale, float sink,
+                                      const float* __restrict__ sink_logit) {
   const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (wid >= rows) return;
   constexpr int EPL = D / 32;
@@ -857,6 +888,7 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_o, const fl
     for (int e = 0; e < EPL; ++e) acc[e] = fmaf(w, part_o[slot * D + lane * EPL + e], acc[e]);
   }
   if (sink > 0.f) L += sink * exp2f(M == -INFINITY ? 0.f : -M);  // a softmax with a sink: its score is 0
+  if (sink_logit != nullptr) L += exp2f(sink_logit[wid % hq] * 1.4426950408889634f - (M == -INFINITY ? 0.f : M));  // a learned sink per head
   const float inv = out_scale / L;
   __nv_bfloat16* dst = out + static_cast<size_t>(wid / hq) * out_ld + (wid % hq) * D;
 #pragma unroll
@@ -868,7 +900,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
                   int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms, int n_splits,
                   void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0, long long q_head_stride = 0,
                   long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0, float out_scale = 1.f, float softcap = 0.f,
-                  float sink = 0.f) {
+                  float sink = 0.f, const MaskExtras& ex = MaskExtras()) {
   using SMEM = Smem<D>;
   const int group = hq / hkv, nt_tile = BM / group;
   // the query tensor: [T][heads][D] rows of the fused projection by default; callers may give the number of heads that exist (a box
@@ -913,7 +945,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.alibi = alibi; p.window = window;
   p.keep = window > 0 ? keep : 0; p.out_ld = out_ld ? out_ld : static_cast<long long>(hq) * D; p.out_scale = out_scale;
   p.cap_l2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; p.cap_in = softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f;
-  p.sink = sink;
+  p.sink = sink; p.sink_logit = ex.sink_logit; p.r1 = ex.r1; p.r2 = ex.r2; p.part = window > 0 ? 0 : ex.part;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   p.trace = nullptr;
@@ -938,7 +970,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   if (n_splits > 1) {
     const int rows = T * hq;
     combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits, hq, p.out_ld,
-                                                                          p.out_scale, p.sink);
+                                                                          p.out_scale, p.sink, p.sink_logit);
     DSB_CHECK_CUDA(cudaGetLastError());
   }
   return DSB_OK;
@@ -949,7 +981,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
                          int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms,
                          int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0,
                          long long q_head_stride = 0, long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0,
-                         float out_scale = 1.f, float softcap = 0.f, float sink = 0.f) {
+                         float out_scale = 1.f, float softcap = 0.f, float sink = 0.f, const MaskExtras& ex = MaskExtras()) {
   constexpr int D = 128;
   const int group = hq / hkv, nt_tile = NQ / group;
   const int heads = q_heads ? q_heads : hq + 2 * hkv;
@@ -987,7 +1019,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.trace = nullptr; p.alibi = alibi; p.window = window;
   p.keep = window > 0 ? keep : 0; p.out_ld = out_ld ? out_ld : static_cast<long long>(hq) * D; p.out_scale = out_scale;
   p.cap_l2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; p.cap_in = softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f;
-  p.sink = sink;
+  p.sink = sink; p.sink_logit = ex.sink_logit; p.r1 = ex.r1; p.r2 = ex.r2; p.part = window > 0 ? 0 : ex.part;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   if (want_trace) {
@@ -1011,7 +1043,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   if (n_splits > 1) {
     const int rows = T * hq;
     combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits, hq, p.out_ld,
-                                                                          p.out_scale, p.sink);
+                                                                          p.out_scale, p.sink, p.sink_logit);
     DSB_CHECK_CUDA(cudaGetLastError());
   }
   return DSB_OK;
@@ -1073,12 +1105,15 @@ DSB_EXPORT int dsb200_paged_flash_decode(const void* qkv, const void* kv_cache, 
 // head-major [heads][T][rank]); the kernel works on `heads` heads (a divisor of 128), the ones past q_heads read as zero.
 // out is [n_tokens][heads][rank] bf16; rank 64 or 128.  decode != 0 selects the small-atom kernel (rank 128, heads dividing 16).
 // Scratch and atoms as for dsb200_paged_flash_attention with hq = heads.
-DSB_EXPORT int dsb200_paged_flash_latent(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride, const void* cache,
-                                         void* out, const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int heads,
-                                         int rank, int block_size, int max_blocks_per_seq, int num_blocks, float scale, int max_atoms,
-                                         int n_splits, void* scratch, int decode, cudaStream_t stream) {
+// sink_logit (null, or `heads` floats): exp(sink_logit[h]) joins head h's softmax denominator, an entry without key and value.
+DSB_EXPORT int dsb200_paged_flash_latent_sink(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride, const void* cache,
+                                              void* out, const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int heads,
+                                              int rank, int block_size, int max_blocks_per_seq, int num_blocks, float scale,
+                                              const float* sink_logit, int max_atoms, int n_splits, void* scratch, int decode, cudaStream_t stream) {
   using namespace dsb;
   if (n_tokens == 0) return DSB_OK;
+  paged::MaskExtras ex;
+  ex.sink_logit = sink_logit;
   DSB_REQUIRE(rank == 64 || rank == 128, "paged_flash_latent: rank %d unsupported (64 or 128)", rank);
   DSB_REQUIRE(heads >= 1 && 128 % heads == 0 && q_heads >= 1 && q_heads <= heads, "paged_flash_latent: %d (%d given) heads must divide 128", heads, q_heads);
   DSB_REQUIRE(q_head_stride % 8 == 0 && q_tok_stride % 8 == 0 && q_head_stride > 0 && q_tok_stride > 0, "paged_flash_latent: query strides must be multiples of 8 elements");
@@ -1087,13 +1122,21 @@ DSB_EXPORT int dsb200_paged_flash_latent(const void* q, int q_heads, long long q
   if (decode) {
     DSB_REQUIRE(rank == 128 && 16 % heads == 0, "paged_flash_latent: the small-atom kernel takes rank 128 and heads dividing 16");
     return paged::launch_decode(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks,
-                                scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
+                                scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1, 0, 0, 1.f, 0.f, 0.f, ex);
   }
   if (rank == 128)
     return paged::launch<128>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks,
-                              scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
+                              scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1, 0, 0, 1.f, 0.f, 0.f, ex);
   return paged::launch<64>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks, scale,
-                           max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
+                           max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1, 0, 0, 1.f, 0.f, 0.f, ex);
+}
+
+DSB_EXPORT int dsb200_paged_flash_latent(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride, const void* cache,
+                                         void* out, const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int heads,
+                                         int rank, int block_size, int max_blocks_per_seq, int num_blocks, float scale, int max_atoms,
+                                         int n_splits, void* scratch, int decode, cudaStream_t stream) {
+  return dsb200_paged_flash_latent_sink(q, q_heads, q_head_stride, q_tok_stride, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, rank,
+                                        block_size, max_blocks_per_seq, num_blocks, scale, nullptr, max_atoms, n_splits, scratch, decode, stream);
 }
 
 // Sliding-window attention that keeps the first keys visible, on the tensor-core kernels: a query at position p sees the keys j <= p with
@@ -1129,12 +1172,19 @@ DSB_EXPORT int dsb200_paged_flash_window(const void* q, long long q_tok_stride, 
 // s_j = scale q . k_j, capped as softcap tanh(s_j / softcap) when softcap > 0 (two more MUFU operations per score).  q [n_tokens][hq][head_dim]
 // bf16 at q_tok_stride elements per token (a multiple of 8), kv_cache [num_blocks][2][block_size][hkv][head_dim] bf16; out rows at out_ld
 // elements per token (a multiple of 8).  decode != 0 selects the small-atom kernel (head_dim 128, q:kv head ratios dividing 16).
-DSB_EXPORT int dsb200_paged_flash_sink(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld, const int* tok_seq,
+// sink_logit (hq floats): learned sinks, exp(sink_logit[h]) joins head h's denominator; r1, r2 (hq floats each): the score of key j for the
+// query at position i loses r1[h] ln(1 + r2[h] (i - j)); part > 0: a query sees only the keys of its own part of `part` positions.  Each may
+// be absent (null / 0).
+DSB_EXPORT int dsb200_paged_flash_sink_ex(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld, const int* tok_seq,
                                        const int* tok_pos, const int* block_table, int n_tokens, int hq, int hkv, int head_dim, int block_size,
-                                       int max_blocks_per_seq, int num_blocks, float scale, float softcap, float sink, int max_atoms, int n_splits,
-                                       void* scratch, int decode, cudaStream_t stream) {
+                                       int max_blocks_per_seq, int num_blocks, float scale, float softcap, float sink, const float* sink_logit,
+                                       const float* r1, const float* r2, int part, int max_atoms, int n_splits, void* scratch, int decode,
+                                       cudaStream_t stream) {
   using namespace dsb;
   if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE((r1 == nullptr) == (r2 == nullptr) && part >= 0 && (r1 == nullptr || softcap == 0.f), "paged_flash_sink: distance term / part %d", part);
+  paged::MaskExtras ex;
+  ex.sink_logit = sink_logit; ex.r1 = r1; ex.r2 = r2; ex.part = part;
   DSB_REQUIRE(head_dim == 64 || head_dim == 128, "paged_flash_sink: head_dim %d unsupported (64 or 128)", head_dim);
   DSB_REQUIRE(hq % hkv == 0 && 128 % (hq / hkv) == 0, "paged_flash_sink: q/kv head ratio %d must divide 128", hq / hkv);
   DSB_REQUIRE(block_size >= 8 && block_size <= 128 && 128 % block_size == 0, "paged_flash_sink: KV block size %d must divide 128", block_size);
@@ -1144,11 +1194,20 @@ DSB_EXPORT int dsb200_paged_flash_sink(const void* q, long long q_tok_stride, co
   if (decode) {
     DSB_REQUIRE(head_dim == 128 && 16 % (hq / hkv) == 0, "paged_flash_sink: the decode kernel takes head_dim 128 and head ratios dividing 16");
     return paged::launch_decode(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
-                                max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink);
+                                max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink, ex);
   }
   if (head_dim == 128)
     return paged::launch<128>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
-                              max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink);
+                              max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink, ex);
   return paged::launch<64>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
-                           max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink);
+                           max_atoms, n_splits, scratch, nullptr, 0, stream, hq, head_dim, q_tok_stride, 2, 0, out_ld, 1.f, softcap, sink, ex);
+}
+
+DSB_EXPORT int dsb200_paged_flash_sink(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld, const int* tok_seq,
+                                       const int* tok_pos, const int* block_table, int n_tokens, int hq, int hkv, int head_dim, int block_size,
+                                       int max_blocks_per_seq, int num_blocks, float scale, float softcap, float sink, int max_atoms, int n_splits,
+                                       void* scratch, int decode, cudaStream_t stream) {
+  return dsb200_paged_flash_sink_ex(q, q_tok_stride, kv_cache, out, out_ld, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, head_dim, block_size,
+                                    max_blocks_per_seq, num_blocks, scale, softcap, sink, nullptr, nullptr, nullptr, 0, max_atoms, n_splits, scratch,
+                                    decode, stream);
 }

@@ -231,6 +231,7 @@ native.register_sigs({
     "dsb200_sandwich_norm": "pp i p ff p f p i pp ii f i p",
     "dsb200_latent_norm_append": "p i pp pp ppp iiii ii f i p",
     "dsb200_paged_flash_latent": "p i ll pp ppp iiiiii f ii p i p",
+    "dsb200_paged_flash_latent_sink": "p i ll pp ppp iiiiii f p ii p i p",
     "dsb200_gate_heads": "pp l p iii i p",
     "dsb200_latent_attention_scratch_floats": "iiii",
     "dsb200_latent_attention": "p i ll p i p ll p ppp ii iii f i p",
@@ -326,15 +327,18 @@ def latent_norm_append(lat, wq, wkv, cache, tok_seq, tok_pos, block_table, nq, n
     return cq
 
 
-def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decode=False, max_context=None, n_splits=None, heads=None):
+def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decode=False, max_context=None, n_splits=None, heads=None,
+                       sink_logit=None):
     """`latent_attention` on the tensor cores (csrc/attn/paged_flash.cu with one cache plane serving as keys and values).
     q_abs: bf16 view [T, H, rank] with unit stride in rank and any 16-byte-multiple token / head strides (token-major, or the
     head-major output of a batched GEMM seen through `.transpose(0, 1)`); rank 64 / 128.  The kernel works on `heads` heads, a divisor
     of 128 that is >= H (default: the next power of two); heads past H read as zero.  cache [blocks, block_size, rank] bf16 with a
     block size dividing 128.  Returns bf16 [T, heads, rank] (rows of heads >= H are meaningless).  `decode`: (almost) one token per
-    sequence -- the small-atom kernel (rank 128, heads dividing 16)."""
+    sequence -- the small-atom kernel (rank 128, heads dividing 16).  `sink_logit` (fp32, one per head the kernel works on): learned sinks,
+    exp(sink_logit[h]) joins head h's softmax denominator."""
     T, H, R = q_abs.shape
     Hp = heads or (1 << (H - 1).bit_length())
+    assert sink_logit is None or (sink_logit.dtype == torch.float32 and sink_logit.numel() >= Hp and sink_logit.is_cuda)
     bs = cache.shape[1]
     assert q_abs.stride(2) == 1 and cache.is_contiguous() and q_abs.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and Hp >= H
     decode = bool(decode) and R == 128 and 16 % Hp == 0
@@ -346,11 +350,11 @@ def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decod
     out = torch.empty(T, Hp, R, dtype=torch.bfloat16, device=q_abs.device)
     nbytes = native.lib().dsb200_paged_flash_scratch_bytes(T, Hp, R, max_atoms, n_splits)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q_abs.device)
-    native.check(native.lib().dsb200_paged_flash_latent(native.ptr(q_abs), H, q_abs.stride(1) if H > 1 else R, q_abs.stride(0) if T > 1 else H * R,
-                                                        native.ptr(cache), native.ptr(out), native.ptr(tok_seq), native.ptr(tok_pos),
-                                                        native.ptr(block_table), T, Hp, R, bs, block_table.shape[1], cache.shape[0], float(scale),
-                                                        max_atoms, n_splits, native.ptr(scratch), int(decode), native.stream_ptr()),
-                 2 + (n_splits > 1))
+    native.check(native.lib().dsb200_paged_flash_latent_sink(native.ptr(q_abs), H, q_abs.stride(1) if H > 1 else R, q_abs.stride(0) if T > 1 else H * R,
+                                                             native.ptr(cache), native.ptr(out), native.ptr(tok_seq), native.ptr(tok_pos),
+                                                             native.ptr(block_table), T, Hp, R, bs, block_table.shape[1], cache.shape[0], float(scale),
+                                                             native.ptr(sink_logit), max_atoms, n_splits, native.ptr(scratch), int(decode),
+                                                             native.stream_ptr()), 2 + (n_splits > 1))
     return out
 
 
@@ -500,6 +504,7 @@ native.register_sigs({
     "dsb200_head_norm_rotary_append": "p l iii pp p f ppp ii p l p l p l iiiii i f i iii i p",
     "dsb200_sink_attention": "p l p l p l ppp ii p l iiiii fff i p",
     "dsb200_paged_flash_sink": "p l pp l ppp iiiiiii fff ii p i p",
+    "dsb200_paged_flash_sink_ex": "p l pp l ppp iiiiiii fff ppp i ii p i p",
 }, restype_long=("dsb200_scan_state_floats", ))
 
 
@@ -697,9 +702,13 @@ def paged_flash_sink_ok(q, cache, out, H, G, d, dv):
             out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and os.environ.get("DSB200_PAGED_FLASH", "1") != "0")
 
 
-def paged_flash_sink(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, scale, softcap=0.0, sink=1.0, decode=False, max_context=None, n_splits=None):
-    """`sink_attention` on the tensor cores (csrc/attn/paged_flash.cu: TMA pages through the block table, S / P / O in TMEM) for a two-plane
-    cache [blocks, 2, block_size, G, d].  `decode`: (almost) one token per sequence -- the small-atom kernel."""
+def paged_flash_sink(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, scale, softcap=0.0, sink=1.0, decode=False, max_context=None, n_splits=None,
+                     sink_logit=None, r1=None, r2=None, part=0):
+    """`sink_attention` / `sink_attention_ex` on the tensor cores (csrc/attn/paged_flash.cu: TMA pages through the block table, S / P / O in
+    TMEM) for a two-plane cache [blocks, 2, block_size, G, d].  `decode`: (almost) one token per sequence -- the small-atom kernel.
+    sink_logit / r1, r2 (fp32 [H]) / part: learned sinks, the logarithmic distance term and the mask by parts, as in `sink_attention_ex`."""
+    for p in (sink_logit, r1, r2):
+        assert p is None or (p.dtype == torch.float32 and p.numel() == H and p.is_cuda)
     T = q.shape[0]
     bs, group = cache.shape[2], H // G
     decode = bool(decode) and d == 128 and 16 % group == 0 and os.environ.get("DSB200_PAGED_DECODE", "1") != "0"
@@ -710,10 +719,11 @@ def paged_flash_sink(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, scal
         n_splits = _pick_splits(T, H, d, max_atoms * G, pages, page_us=0.45 if decode else 0.7)
     nbytes = native.lib().dsb200_paged_flash_scratch_bytes(T, H, d, max_atoms, n_splits)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-    native.check(native.lib().dsb200_paged_flash_sink(native.ptr(q), q.stride(0), native.ptr(cache), native.ptr(out), out.stride(0), native.ptr(tok_seq),
-                                                      native.ptr(tok_pos), native.ptr(block_table), T, H, G, d, bs, block_table.shape[1], cache.shape[0],
-                                                      float(scale), float(softcap), float(sink), max_atoms, n_splits, native.ptr(scratch), int(decode),
-                                                      native.stream_ptr()), 2 + (n_splits > 1))
+    native.check(native.lib().dsb200_paged_flash_sink_ex(native.ptr(q), q.stride(0), native.ptr(cache), native.ptr(out), out.stride(0), native.ptr(tok_seq),
+                                                         native.ptr(tok_pos), native.ptr(block_table), T, H, G, d, bs, block_table.shape[1],
+                                                         cache.shape[0], float(scale), float(softcap), float(sink), native.ptr(sink_logit),
+                                                         native.ptr(r1), native.ptr(r2), int(part), max_atoms, n_splits, native.ptr(scratch),
+                                                         int(decode), native.stream_ptr()), 2 + (n_splits > 1))
     return out
 
 

@@ -64,6 +64,14 @@ class KeyUpParameter(ParameterBase):
         return self.inference_model.transform_key_up_param(self.params, self.layer_index)
 
 
+class HeadSinkParameter(ParameterBase):
+    """One sink score per head of a latent-attention mixer (padded to the heads its kernel works on)."""
+    params: torch.Tensor
+
+    def finalize(self) -> torch.Tensor:
+        return self.inference_model.transform_head_sink_param(self.params, self.layer_index)
+
+
 class ValueUpParameter(ParameterBase):
     params: torch.Tensor
 
@@ -138,7 +146,7 @@ class MidulornLatentContainer(_MidulornLayerContainer):
     kv_norm: Fp32Parameter
     key_up: KeyUpParameter
     value_up: ValueUpParameter
-    sink: Fp32Parameter
+    sink: HeadSinkParameter
 
     PARAM_MAPPING = {
         "mix.q": "in_w.q",

@@ -250,6 +250,9 @@ class MidulornInferenceModel(RaggedTransformer, DSInferenceModelBase):
     def transform_value_up_param(self, param, layer_index):
         return self._dev(self.attn_mods[layer_index].transform_value_up_param(param))
 
+    def transform_head_sink_param(self, param, layer_index):
+        return self._dev(self.attn_mods[layer_index].transform_sink_param(param))
+
     def _any_moe(self):
         mods = [m for m in self.moe_mods if m is not None]
         assert mods, "an expert tensor arrived for a model without mixture-of-experts layers"

@@ -45,7 +45,7 @@ class DSConvSinkAttention(DSSelfAttentionBase):
         super().__init__(config, implementation_config)
         self._dtype = DtypeEnum(config.input_dtype).value
         widest = max(config.head_size, config.value_size)
-        flash = self._dtype == torch.bfloat16 and widest <= 128 and os.environ.get("DSB200_CONV_ATTN_FLASH", "0") != "0"
+        flash = self._dtype == torch.bfloat16 and widest <= 128 and os.environ.get("DSB200_CONV_ATTN_FLASH", "1") != "0"
         self._pad = (64 if widest <= 64 else 128) if flash else None  # common width of all heads on the tensor-core path
 
     @property

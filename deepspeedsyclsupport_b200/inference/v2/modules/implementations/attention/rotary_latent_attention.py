@@ -51,7 +51,7 @@ class DSRotaryLatentAttention(DSSelfAttentionBase):
         self._freq_host = torch.tensor([float(c.theta_base)**(-2.0 * i / c.rotate_dim) for i in range(half)], dtype=torch.float64)
         self._freq = None
         used = c.kv_rank + c.rot_dim
-        self._flash = (self._dtype == torch.bfloat16 and used <= 128 and c.n_heads <= 128 and os.environ.get("DSB200_ROTARY_LATENT_FLASH", "0") != "0")
+        self._flash = (self._dtype == torch.bfloat16 and used <= 128 and c.n_heads <= 128 and os.environ.get("DSB200_ROTARY_LATENT_FLASH", "1") != "0")
         self._row = (64 if used <= 64 else 128) if self._flash else used  # width of a cached row
         self._heads_p = 1
         while self._heads_p < c.n_heads:
@@ -81,6 +81,13 @@ class DSRotaryLatentAttention(DSSelfAttentionBase):
     # ---- parameter layouts
     def transform_fp32_param(self, param: torch.Tensor) -> InferenceParameter:
         return InferenceParameter.initialize(param.to(torch.float32).contiguous())
+
+    def transform_sink_param(self, param: torch.Tensor) -> InferenceParameter:
+        """One sink score per head, fp32; padded to the heads the tensor-core kernel works on."""
+        w = param.to(torch.float32).reshape(-1)
+        if self._flash and self._heads_p > w.numel():
+            w = torch.nn.functional.pad(w, (0, self._heads_p - w.numel()))
+        return InferenceParameter.initialize(w.contiguous())
 
     def transform_key_up_param(self, param: torch.Tensor) -> InferenceParameter:
         """[heads * qk_dim, kv_rank] -> [heads, qk_dim + rot_dim, row]: right operand of the per-head map (q_h | q_rot,h) -> (U_h^T q_h | q_rot,h)."""
@@ -127,7 +134,7 @@ class DSRotaryLatentAttention(DSSelfAttentionBase):
             att = torch.empty(H, T, W, dtype=self._dtype, device=proj.device)
             plane = (cache, cache.stride(0))
             K.sink_attention_ex(qa.transpose(0, 1), qa.stride(0), plane, R, plane, R, tok_seq, tok_pos, bt, bs, att.transpose(0, 1), att.stride(0), H, 1,
-                                R, W, c.scale, sink_logit=sink)
+                                R, W, c.scale, sink_logit=sink[:H] if sink is not None else None)
             o = _bmm(att, value_up_w, self._dtype)  # [H, T, v_dim]
         if c.head_gate:
             return K.gate_heads_scalar(o.contiguous(), proj[:, g0:g0 + H], out)  # heads side by side per token and the gate, one pass

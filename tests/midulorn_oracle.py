@@ -178,3 +178,119 @@ def forward(tokens, sd, cfg):
         streams.append(x)
     logits = rms_norm(x, sd["final.norm"], eps) @ sd["embed"].to(F64).T * cfg["logit_scale"]
     return logits, torch.stack(streams)
+
+
+# ------------------------------------------------------------------------------------------------ small models for the tests
+def latent_layer(heads, dim, rot_dim, vdim, kv_rank, scale=None, rot_dims=None, base=10000.0, mlp=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": scale if scale is not None else (dim + rot_dim)**-0.5,
+         "rot": {"dims": rot_dim if rot_dims is None else rot_dims, "base": base}}
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def mingru_layer(width, mlp=None):
+    return {"type": "mingru", "mixer": {"width": width}, "mlp": mlp}
+
+
+def attention_layer(heads, kv_heads, dim, vdim, conv=3, part=16, scale=None, v_mix=False, mlp=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "mask": {"size": part}, "scale": scale if scale is not None else dim**-0.5,
+         "v_mix": v_mix}
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(experts, top, ff):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def make_config(layers, vocab=64, width=32, eps=1e-5, alpha=1.5, embedding_scale=2.0, logit_scale=0.7):
+    return {"architecture": "Midulorn", "vocab": vocab, "width": width, "norm": {"eps": eps}, "postln_alpha": alpha,
+            "embedding": {"scale": embedding_scale}, "logit_scale": logit_scale, "layers": layers}
+
+
+def random_weights(cfg, seed=0, router_gain=4.0):
+    """bf16 tensors under the family's names.  Projections ~ N(0, 1 / fan_in) so that activations stay O(1); norm weights around 1; gate
+    biases spread so that slow and fast channels both occur; router rows scaled up so that selections are decided."""
+    g = torch.Generator().manual_seed(seed)
+    D = cfg["width"]
+
+    def lin(o, i, gain=1.0):
+        return (torch.randn(o, i, generator=g) * gain * i**-0.5).bfloat16()
+
+    def around_one(n):
+        return (1.0 + 0.2 * torch.randn(n, generator=g)).bfloat16()
+
+    def small(*shape, gain=0.3):
+        return (gain * torch.randn(*shape, generator=g)).bfloat16()
+
+    w = {"embed": (torch.randn(cfg["vocab"], D, generator=g) * 0.5).bfloat16(), "final.norm": around_one(D)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        w[p + "norm1"] = around_one(D)
+        if L["type"] == "latent_attention":
+            H, d, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            w.update({p + "mix.q": lin(H * (d + dr), D, 2.0), p + "mix.dkv": lin(R + dr, D, 2.0), p + "mix.dkv.norm": around_one(R), p + "mix.uk": lin(H * d, R, 2.0),
+                      p + "mix.uv": lin(H * dv, R), p + "mix.sink": small(H, gain=1.0), p + "mix.g": lin(H, D, 2.0), p + "mix.o": lin(D, H * dv)})
+        elif L["type"] == "mingru":
+            n = m["width"]
+            w.update({p + "mix.z": lin(n, D, 2.0), p + "mix.z.b": (torch.randn(n, generator=g) * 2.0 - 1.0).bfloat16(), p + "mix.x": lin(n, D, 2.0),
+                      p + "mix.x.b": small(n), p + "mix.g": lin(n, D, 2.0), p + "mix.o": lin(D, n)})
+        else:
+            H, G, d, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for name, n in (("q", H * d), ("k", G * d), ("v", G * dv)):
+                w[p + f"mix.{name}"] = lin(n, D, 2.0)
+                w[p + f"mix.{name}.b"] = small(n)
+                w[p + f"mix.{name}.conv"] = (torch.randn(n, taps, generator=g) * taps**-0.5 + (torch.arange(taps) == taps - 1) * 0.5).bfloat16()
+            w.update({p + "mix.q.norm": around_one(d), p + "mix.k.norm": around_one(d), p + "mix.vmix": torch.tensor(0.35).bfloat16(),
+                      p + "mix.r1": (0.5 + torch.rand(H, generator=g)).bfloat16(), p + "mix.r2": (0.1 + torch.rand(H, generator=g)).bfloat16(),
+                      p + "mix.sink": small(H, gain=1.0), p + "mix.o": lin(D, H * dv), p + "mix.o.b": small(D)})
+        f = L["mlp"]
+        if f is None:
+            continue
+        w[p + "norm2"] = around_one(D)
+        if f["kind"] == "dense":
+            w.update({p + "mlp.up": lin(f["ff"], D, 2.0), p + "mlp.down": lin(D, f["ff"]), p + "mlp.act": torch.tensor([0.4, -0.3]).bfloat16()})
+        else:
+            w[p + "mlp.router"] = lin(f["router"]["experts"], D, router_gain)
+            for e in range(f["router"]["experts"]):
+                w.update({p + f"mlp.e{e}.gate": lin(f["expert"]["ff"], D, 2.0), p + f"mlp.e{e}.up": lin(f["expert"]["ff"], D, 2.0),
+                          p + f"mlp.e{e}.down": lin(D, f["expert"]["ff"])})
+    return w
+
+
+def run(cfg, w, tokens, collect_layers=False):
+    logits, streams = forward(tokens, w, cfg)
+    return (logits, list(streams)) if collect_layers else logits
+
+
+def greedy(cfg, w, prompt, n_new):
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(toks, w, cfg)[0][-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+def write_model(folder, cfg, w):
+    """config.json + model.safetensors (8-byte little-endian header length, JSON header, raw little-endian data) -> folder."""
+    import json
+    import os
+    import struct
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as fh:
+        json.dump(cfg, fh)
+    names = {torch.bfloat16: "BF16", torch.float32: "F32", torch.int32: "I32"}
+    header, blobs, at = {}, [], 0
+    for k, t in w.items():
+        raw = t.contiguous().reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[k] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as fh:
+        fh.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    return folder
