@@ -35,9 +35,10 @@ def parse():
     p.add_argument("--no-act-ckpt", action="store_true")
     p.add_argument("--zero-stage", type=int, default=3)
     p.add_argument("--zeropp", action="store_true", help="ZeRO++: zero_quantized_weights + zero_quantized_gradients (config #2, second half)")
-    p.add_argument("--workload", default="llama7b", choices=["llama7b", "fastgen70b", "mixtral", "ulysses13b", "linasun", "kulanex", "pudinex"],
+    p.add_argument("--workload", default="llama7b", choices=["llama7b", "fastgen70b", "mixtral", "ulysses13b", "linasun", "kulanex", "pudinex", "midulorn"],
                    help="llama7b = the headline (config #2); fastgen70b / mixtral / ulysses13b are the end-to-end runs of configs #5 / #4 / #3; "
-                        "linasun / kulanex / pudinex = FastGen prefill / decode of that family beside a Mixtral (pudinex: also a Kulanex) of equal size, 1 GPU "
+                        "linasun / kulanex / pudinex / midulorn = FastGen prefill / decode of that family beside a Mixtral (pudinex: also a Kulanex; midulorn: also a "
+                        "Pudinex) of equal size, 1 GPU "
                         "(--model s,m,l picks sizes)")
     p.add_argument("--quant", default="", help="fastgen70b: '' (bf16) | wf8af8_mx | wf8af8_block | wf8af8")
     p.add_argument("--sequences", type=int, default=64, help="fastgen70b: concurrent sequences")

@@ -979,4 +979,261 @@ def run_pudinex(args):
           flush=True)
 
 
-WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun, "kulanex": run_kulanex, "pudinex": run_pudinex}
+MIDULORN_SIZES = PUDINEX_SIZES  # the same widths, heads, experts and vocabularies: the twins are built from one tuple
+MIDULORN_ROT = 32  # rotated entries per query head of the latent-attention layers (their latent has head_dim - 32 values: a cached row of head_dim)
+MIDULORN_TAPS, MIDULORN_PART = 4, 1024
+
+
+def _midulorn_state(torch, dev, W, L, H, d, hkv, E, top, ff, V):
+    """Layers cycle 'latent_attention' (H heads of d - 32 plain + 32 rotated entries, values of d, latent of d - 32 beside a rotated key part of
+    32: a cached row of d), 'mingru' (width H d), 'attention' (H:hkv heads of d behind 4 taps, parts of 1024, values mixed with the first such
+    layer's), 'mingru'; every layer with the MoE feed-forward (E experts, top) but the last, whose feed-forward is dense (xIELU, hidden E ff / 2)."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top}}
+    dense = {"kind": "dense", "ff": E * ff // 2}
+    rot, n = MIDULORN_ROT, H * d
+    lat = {"type": "latent_attention", "mixer": {"heads": H, "dim": d - rot, "rot_dim": rot, "vdim": d, "kv_rank": d - rot, "scale": d ** -0.5,
+                                                 "rot": {"base": 1e6, "dims": rot}}}
+    rec = {"type": "mingru", "mixer": {"width": n}}
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": hkv, "dim": d, "vdim": d, "conv": MIDULORN_TAPS, "mask": {"size": MIDULORN_PART},
+                                          "scale": d ** -0.5, "v_mix": True}}
+    kinds = [lat, rec, att, rec]
+    layers = [dict(kinds[i % 4], mlp=dense if i == L - 1 else moe) for i in range(L)]
+    cfg = {"architecture": "Midulorn", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": W ** 0.5}, "postln_alpha": 2.0,
+           "logit_scale": 0.5, "layers": layers}
+
+    def r(*shape, std=0.02, mean=0.0):
+        return torch.empty(*shape, device=dev, dtype=torch.bfloat16).normal_(mean, std)
+
+    sd = {"embed": r(V, W, std=0.05), "final.norm": r(W, mean=1.0)}
+    for i, Lc in enumerate(layers):
+        p, a = f"l{i}.", f"l{i}.mix."
+        sd.update({p + "norm1": r(W, mean=1.0), p + "norm2": r(W, mean=1.0)})
+        if Lc["mlp"]["kind"] == "moe":
+            sd[p + "mlp.router"] = r(E, W, std=0.5)
+            for e in range(E):
+                sd.update({p + f"mlp.e{e}.gate": r(ff, W), p + f"mlp.e{e}.up": r(ff, W), p + f"mlp.e{e}.down": r(W, ff)})
+        else:
+            sd.update({p + "mlp.up": r(dense["ff"], W), p + "mlp.down": r(W, dense["ff"]), p + "mlp.act": r(2, std=0.5)})
+        if Lc["type"] == "latent_attention":
+            sd.update({a + "q": r(H * d, W), a + "dkv": r(d, W), a + "dkv.norm": r(d - rot, mean=1.0), a + "uk": r(H * (d - rot), d - rot, std=0.1),
+                       a + "uv": r(H * d, d - rot, std=0.1), a + "sink": r(H, std=1.0), a + "g": r(H, W), a + "o": r(W, H * d)})
+        elif Lc["type"] == "mingru":
+            sd.update({a + "z": r(n, W), a + "z.b": r(n, mean=-1.0, std=1.0), a + "x": r(n, W), a + "x.b": r(n), a + "g": r(n, W), a + "o": r(W, n)})
+        else:
+            for nm, c in (("q", H * d), ("k", hkv * d), ("v", hkv * d)):
+                sd.update({a + nm: r(c, W), a + nm + ".b": r(c), a + nm + ".conv": r(c, MIDULORN_TAPS, std=0.5)})
+            sd.update({a + "q.norm": r(d, mean=1.0), a + "k.norm": r(d, mean=1.0), a + "vmix": r(1, mean=0.3, std=0.0).reshape(()), a + "r1": r(H, mean=1.0, std=0.1),
+                       a + "r2": r(H, mean=0.5, std=0.05), a + "sink": r(H, std=1.0), a + "o": r(W, H * d), a + "o.b": r(W)})
+    return cfg, sd
+
+
+def _midulorn_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, T, ctx, n_dec):
+    """Every kernel of the design beside the like kernel of the closest family (Pudinex; Linasun for the latent rows, Kulanex for the convolving
+    prepare), isolated, with the fraction of the measured roofline (HBM copy bandwidth for the streaming kernels, cuBLAS bf16 rate for attention
+    prefill)."""
+    from deepspeedsyclsupport_b200.inference.v2 import kernels as K
+    from deepspeedsyclsupport_b200.ops import fused_ops as FO
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, ms, like, like_ms, nbytes=None, like_bytes=None, flops=None, like_flops=None):
+        def frac(ms_, b, f):
+            return round(max((b or 0) / hbm, (f or 0) / tf) / (ms_ * 1e-3), 3)
+        rows.append({"kernel": name, "ms": round(ms, 4), "roofline_frac": frac(ms, nbytes, flops), "like": like, "like_ms": round(like_ms, 4),
+                     "like_roofline_frac": frac(like_ms, like_bytes if like_bytes is not None else nbytes, like_flops if like_flops is not None else flops)})
+
+    rot, n = MIDULORN_ROT, H * d
+    x32, y, y32, g32 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev), torch.randn(W, device=dev)
+    add("post_sum_norm (bf16 branch + bias in; fp32 stream and bf16 copy out)", _event_ms(torch, lambda: K.post_sum_norm(x32, y, g32, 2.0, 1e-6, bias=g32), 20, flush),
+        "stream_group_norm (2 parts; bf16 branch in, bf16 out; Pudinex)", _event_ms(torch, lambda: K.stream_group_norm(x32, (y, ), None, g32, 2, 1e-6), 20, flush),
+        nbytes=T * W * (4 + 2 + 4 + 2))
+    add("post_sum_norm (fp32 branch of the experts in)", _event_ms(torch, lambda: K.post_sum_norm(x32, None, g32, 2.0, 1e-6, y32=y32), 20, flush),
+        "stream_group_norm (fp32 branch in; Pudinex)", _event_ms(torch, lambda: K.stream_group_norm(x32, (), y32, g32, 2, 1e-6), 20, flush),
+        nbytes=T * W * (4 + 4 + 4 + 2))
+    F = E * ff // 2
+    up, gpair, coef = torch.randn(T, F, device=dev).to(bf), torch.randn(T, 2 * F, device=dev).to(bf), K.xielu_coefficients(0.3, -0.2).to(dev)
+    add("xielu", _event_ms(torch, lambda: K.xielu(up, coef), 20, flush), "gated_act (silu; Mixtral)", _event_ms(torch, lambda: FO.gated_act(gpair, "silu"), 20, flush),
+        nbytes=T * F * 4, like_bytes=T * F * 6)
+    lg = torch.randn(T, E, device=dev)
+    add("grouped_topk_gating (softmax, not renormalised)", _event_ms(torch, lambda: K.grouped_topk_gating(lg, top), 20, flush),
+        "grouped_topk_gating (softmax, renormalised; Pudinex)", _event_ms(torch, lambda: K.grouped_topk_gating(lg, top, normalize=True), 20, flush),
+        nbytes=T * (E * 4 + top * 12))
+    a3, gh, gfull = torch.randn(H, T, d, device=dev).to(bf), torch.randn(T, H, device=dev).to(bf), torch.randn(T, H * d, device=dev).to(bf)
+    add("gate_heads_scalar (one gate per token and head)", _event_ms(torch, lambda: K.gate_heads_scalar(a3, gh), 20, flush),
+        "gate_heads (one gate per value; Linasun)", _event_ms(torch, lambda: K.gate_heads(a3, gfull), 20, flush), nbytes=T * n * 4, like_bytes=T * n * 6)
+    bs = 128
+    from deepspeedsyclsupport_b200.inference.v2.modules.configs import RampRotaryScalingConfig
+    from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.sink_blocked_attention import ramp_scaled_frequencies
+    pfreq, pmag = ramp_scaled_frequencies(d // 2, 1e6, RampRotaryScalingConfig(factor=8.0, original=8192, fast=32.0, slow=1.0))
+    pfreq = pfreq.to(dev)
+    lfreq = torch.tensor([1e6 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64, device=dev)
+    Hp = 1 << (H - 1).bit_length()
+    for label, n_seq, new, seen in (("prefill", max(1, T // 2048), min(T, 2048), ctx), ("decode", n_dec, 1, ctx)):
+        per = -(-(seen + new) // bs)
+        nb = n_seq * per
+        bt = torch.arange(nb, dtype=torch.int32, device=dev).view(n_seq, per)
+        tok_seq = torch.arange(n_seq, dtype=torch.int32, device=dev).repeat_interleave(new)
+        tok_pos = (seen + torch.arange(new, dtype=torch.int32, device=dev)).repeat(n_seq)
+        desc = torch.tensor([[i * new, new, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        Tn = n_seq * new
+        dec = label == "decode"
+        kv = torch.randn(nb, 2, bs, hkv, d, device=dev).to(bf)
+        qkv = torch.randn(Tn, (H + 2 * hkv) * d, device=dev).to(bf)
+        nw = torch.randn(d, device=dev)
+        qo = torch.empty(Tn, H * d, device=dev, dtype=bf)
+        planes = K.cache_planes(kv)
+        C = (H + 2 * hkv) * d
+        cw, cb, mix = torch.randn(C, MIDULORN_TAPS, device=dev), torch.randn(C, device=dev), torch.full((1, ), 0.3, device=dev)
+        cstate = torch.zeros(n_seq, MIDULORN_TAPS - 1, C, device=dev, dtype=bf)
+        vsrc = torch.randn(Tn, hkv * d, device=dev).to(bf)
+
+        def cprep():
+            K.conv_head_norm_append(qkv, 0, cb, cw, nw, nw, cstate, desc, tok_seq, tok_pos, bt, bs, planes[0], planes[1], qo, H, hkv, d, d, MIDULORN_TAPS, 1e-6,
+                                    v_other=vsrc, mix=mix)
+            K.conv_state_update(qkv, 0, C, cstate, 0, desc, n_seq, MIDULORN_TAPS)
+        add(f"conv_head_norm_append + conv_state_update, {label}", _event_ms(torch, cprep, 10, flush), f"head_norm_rotary_append (Pudinex), {label}",
+            _event_ms(torch, lambda: K.head_norm_rotary_append(qkv, 0, H * d, (H + hkv) * d, nw, nw, pfreq, pmag, tok_seq, tok_pos, bt, bs, planes[0], planes[1], qo,
+                                                               H, hkv, d, d, d // 2, 1e-6), 10, flush),
+            nbytes=Tn * (C * 4 + hkv * d * 2), like_bytes=Tn * C * 4)
+        keys = n_seq * new * (seen + (new + 1) / 2)
+        out = torch.empty(Tn, H * d, device=dev, dtype=bf)
+        abytes = n_seq * (seen + new) * hkv * d * 4 + Tn * H * d * 4
+        r1, r2, sk = torch.full((H, ), 1.0, device=dev), torch.full((H, ), 0.5, device=dev), torch.randn(H, device=dev)
+        ms_like = _event_ms(torch, lambda: K.paged_flash_sink(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, d ** -0.5, 50.0, 1.0, decode=dec), 10, flush)
+        add(f"attention, distance term + learned sinks, one part, tcgen05, {label} (GQA {H}:{hkv})",
+            _event_ms(torch, lambda: K.paged_flash_sink(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, d ** -0.5, 0.0, 0.0, decode=dec, sink_logit=sk, r1=r1, r2=r2,
+                                                        part=1 << 20), 10, flush),
+            f"attention, soft cap 50 + sink, tcgen05, {label} (Pudinex)", ms_like, nbytes=abytes, flops=4.0 * keys * H * d)
+        # parts of 1024: a query sees at most its own part, so the kernel visits a fraction of the pages (the work shrinks with it)
+        pk = n_seq * sum(min(p % MIDULORN_PART + 1, p + 1) for p in range(seen, seen + new))
+        pbytes = n_seq * min(seen + new, MIDULORN_PART + new) * hkv * d * 4 + Tn * H * d * 4
+        add(f"attention, distance term + learned sinks, parts of {MIDULORN_PART}, tcgen05, {label}",
+            _event_ms(torch, lambda: K.paged_flash_sink(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, d ** -0.5, 0.0, 0.0, decode=dec, sink_logit=sk, r1=r1, r2=r2,
+                                                        part=MIDULORN_PART), 10, flush),
+            f"attention, soft cap 50 + sink, tcgen05, {label} (Pudinex; whole context)", ms_like, nbytes=pbytes, like_bytes=abytes, flops=4.0 * pk * H * d,
+            like_flops=4.0 * keys * H * d)
+        # low-rank rows: rotation + norm + append, then one-plane attention with sinks, beside the same without rotation / sinks
+        lat = torch.randn(Tn, H * d + d + H, device=dev).to(bf)
+        lcache = torch.randn(nb, bs, d, device=dev).to(bf)
+        wkv = torch.randn(d - rot, device=dev)
+        lat2 = torch.randn(Tn, 2 * d, device=dev).to(bf)
+        wq2 = torch.randn(d, device=dev)
+        add(f"latent_rotary_append, {label}", _event_ms(torch, lambda: K.latent_rotary_append(lat, 0, H * d, wkv, lfreq, tok_seq, tok_pos, bt, lcache, H, d - rot, rot,
+                                                                                            d - rot, rot, 1e-6), 10, flush),
+            f"latent_norm_append (Linasun), {label}", _event_ms(torch, lambda: K.latent_norm_append(lat2, wq2, wq2, lcache, tok_seq, tok_pos, bt, d, d, 1e-6), 10, flush),
+            nbytes=Tn * (H * rot * 4 + d * 4), like_bytes=Tn * d * 8)
+        qa = torch.randn(Hp, Tn, d, device=dev).to(bf)
+        skp = torch.randn(Hp, device=dev)
+        lbytes = n_seq * (seen + new) * d * 2 + Tn * Hp * d * 4
+        add(f"latent attention with learned sinks, tcgen05 one-plane, {label} ({Hp} heads)",
+            _event_ms(torch, lambda: K.paged_latent_flash(qa.transpose(0, 1), lcache, tok_seq, tok_pos, bt, d ** -0.5, decode=dec, heads=Hp, sink_logit=skp), 10, flush),
+            f"latent attention, tcgen05 one-plane, {label} (Linasun)",
+            _event_ms(torch, lambda: K.paged_latent_flash(qa.transpose(0, 1), lcache, tok_seq, tok_pos, bt, d ** -0.5, decode=dec, heads=Hp), 10, flush),
+            nbytes=lbytes, flops=4.0 * keys * Hp * d)
+        # the recurrence beside Pudinex's scan: one number of state per channel against a d x d matrix per head
+        proj = torch.randn(Tn, 3 * n, device=dev).to(bf)
+        zb = torch.zeros(n, device=dev)
+        sS = torch.zeros(n_seq, n, device=dev)
+        og = torch.empty(Tn, n, device=dev, dtype=bf)
+        fb, lo = torch.full((n, ), 2.0, device=dev), torch.full((n, ), 0.5, device=dev)
+        tS = torch.zeros(n_seq, H, K.scan_state_floats(d, d), device=dev)
+        ms_like = _event_ms(torch, lambda: K.tied_gate_scan(proj, 0, n, 2 * n, fb, lo, desc, n_seq, tS, H, d, d), 5, flush)
+        add(f"mingru_scan (width {n}), {label}", _event_ms(torch, lambda: K.mingru_scan(proj, 0, n, 2 * n, zb, zb, tok_seq, desc, n_seq, sS, og, n), 10, flush),
+            f"tied_gate_scan ({H} x {d} x {d}; Pudinex), {label}", ms_like, nbytes=Tn * n * (3 * 2 + 2) + n_seq * n * 8,
+            like_bytes=Tn * n * (3 * 2 + 4) + n_seq * H * d * d * 8)
+        if not dec:
+            add(f"mingru_scan as one walk per sequence (width {n}), {label}",
+                _event_ms(torch, lambda: K.mingru_scan(proj, 0, n, 2 * n, zb, zb, tok_seq, desc, n_seq, sS, og, n, pieces=False), 5, flush),
+                f"tied_gate_scan ({H} x {d} x {d}; Pudinex), {label}", ms_like, nbytes=Tn * n * (3 * 2 + 2) + n_seq * n * 8,
+                like_bytes=Tn * n * (3 * 2 + 4) + n_seq * H * d * d * 8)
+    return rows
+
+
+def run_midulorn(args):
+    """Prefill and decode throughput of Midulorn through the FastGen engine at a few layer sizes, beside a Pudinex (the closest family: attention
+    with sinks on per-head normed queries and keys, recurrent layers in the state slots, softmax router) and a Mixtral of equal size (same width,
+    layers, heads, experts, ff, top-k, vocabulary), plus the isolated kernels of the design beside their likes."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import deepspeedsyclsupport_b200 as deepspeed
+    from deepspeedsyclsupport_b200 import comm as dist
+    from deepspeedsyclsupport_b200.inference.v2 import RaggedInferenceEngineConfig, build_engine_from_state_dict
+    from deepspeedsyclsupport_b200.ops import native
+    deepspeed.init_distributed()
+    assert dist.get_world_size() == 1, "--workload midulorn is a one-GPU comparison"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        peaks = dict(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), source="measured")
+    n_seqs, prompt, budget = min(args.sequences, 64), 1024, 4096
+    results, clocks, l0 = {}, None, native.launch_count
+    g = torch.Generator().manual_seed(11)
+    for name in (args.model.split(",") if args.model != "7b" else ["s", "m"]):
+        W, L, H, d, hkv, E, top, ff, V = MIDULORN_SIZES[name]
+        max_ctx = -(-(prompt + 4 * (args.steps + args.warmup) * 4 + 64) // 128) * 128
+        ecfg = RaggedInferenceEngineConfig(state_manager={"max_ragged_batch_size": budget, "max_ragged_sequence_count": n_seqs, "max_tracked_sequences": n_seqs,
+                                                          "max_context": max_ctx, "memory_config": {"mode": "allocate", "size": n_seqs * (max_ctx // 128) + 4}})
+        res = {}
+        for fam in ("midulorn", "pudinex", "mixtral"):
+            if fam == "midulorn":
+                cfg, sd = _midulorn_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            elif fam == "pudinex":
+                cfg, sd = _pudinex_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            else:
+                cfg, sd = _mixtral_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            eng = build_engine_from_state_dict(fam, cfg, sd, ecfg, dtype=torch.bfloat16)
+            n_params = sum(v.numel() for v in sd.values())
+            del sd
+            prompts = [torch.randint(0, V, (prompt, ), generator=g).pin_memory() for _ in range(n_seqs)]
+            uids = list(range(n_seqs))
+            state = {"live": False, "next": None}
+
+            def prefill():
+                if state["live"]:
+                    for u in uids:
+                        eng.flush(u)
+                per = budget // prompt
+                nxt = torch.zeros(n_seqs, dtype=torch.long)
+                for i in range(0, n_seqs, per):
+                    us = uids[i:i + per]
+                    nxt[i:i + len(us)] = eng.put(us, [prompts[u] for u in us]).argmax(-1).cpu()
+                state["live"], state["next"] = True, nxt
+
+            def decode():
+                nxt = state["next"]
+                for _ in range(4):
+                    nxt = eng.put(uids, [nxt[u:u + 1] for u in uids]).argmax(-1).cpu()
+                state["next"] = nxt
+
+            ms_p, _ = _timed(torch, dist, prefill, args.steps, 3)
+            ms_d, clk = _timed(torch, dist, decode, args.steps, args.warmup)
+            if fam == "midulorn":
+                clocks = clk
+            res[fam] = {"params_b": round(n_params / 1e9, 3), "prefill_tokens_per_s": round(n_seqs * prompt / ms_p * 1e3, 1), "prefill_ms": round(ms_p, 2),
+                        "decode_tokens_per_s": round(n_seqs * 4 / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d / 4, 3)}
+            del eng
+            torch.cuda.empty_cache()
+        for other in ("pudinex", "mixtral"):
+            res["midulorn_over_" + other] = {"prefill": round(res["midulorn"]["prefill_tokens_per_s"] / res[other]["prefill_tokens_per_s"], 3),
+                                             "decode": round(res["midulorn"]["decode_tokens_per_s"] / res[other]["decode_tokens_per_s"], 3)}
+        res["shape"] = {"width": W, "layers": L, "heads": H, "head_dim": d, "kv_heads": hkv, "experts": E, "top": top, "ff": ff, "rotated": MIDULORN_ROT,
+                        "taps": MIDULORN_TAPS, "part": MIDULORN_PART}
+        res["kernels"] = _midulorn_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, 4096, 2048, n_seqs)
+        results[name] = res
+    launches = native.launch_count - l0
+    last = results[list(results)[-1]]
+    extra = {"results": results, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops", "source")},
+             "e2e": {"value": last["midulorn"]["decode_tokens_per_s"], "unit": "generated tokens/s", "h2d_bytes_per_step": n_seqs * 8, "d2h_bytes_per_step": n_seqs * 8},
+             "reference_arm": "none: the reference has no model of this design"}
+    config = {"model": "midulorn (random weights) beside pudinex and mixtral of equal size", "sizes": list(results), "sequences": n_seqs, "prompt_len": prompt,
+              "token_budget_per_forward": budget, "decode_steps_per_timed_step": 4, "kv_block": 128,
+              "l2_policy": "engine steps: weights exceed the 126 MB L2, no flush; isolated kernels: 256 MB write before every timed run"}
+    print(json.dumps(_line("generated tokens/sec Midulorn FastGen ragged decode, 1 GPU (prefill, a Pudinex and a Mixtral of equal size alongside)",
+                           last["midulorn"]["decode_tokens_per_s"], "tokens/s", 1, args, last["midulorn"]["decode_ms_per_step"], config, clocks, launches, extra)),
+          flush=True)
+
+
+WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun, "kulanex": run_kulanex, "pudinex": run_pudinex, "midulorn": run_midulorn}

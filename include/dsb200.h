@@ -150,7 +150,13 @@ int dsb200_paged_flash_decode(const void* qkv, const void* kv_cache, void* out, 
  * `rank` values per token at element strides q_head_stride / q_tok_stride (multiples of 8; token-major [T][heads][rank] or
  * head-major [heads][T][rank]); the kernel works on `heads` heads (a divisor of 128), the ones past q_heads read as zero.
  * out is [n_tokens][heads][rank] bf16; rank 64 or 128.  decode != 0 selects the small-atom kernel (rank 128, heads dividing 16).
- * Scratch and atoms as for dsb200_paged_flash_attention with hq = heads. */
+ * Scratch and atoms as for dsb200_paged_flash_attention with hq = heads.
+ * sink_logit (null, or `heads` floats): exp(sink_logit[h]) joins head h's softmax denominator, an entry without key and value. */
+int dsb200_paged_flash_latent_sink(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride,
+                                   const void* cache, void* out, const int* tok_seq, const int* tok_pos,
+                                   const int* block_table, int n_tokens, int heads, int rank, int block_size,
+                                   int max_blocks_per_seq, int num_blocks, float scale, const float* sink_logit,
+                                   int max_atoms, int n_splits, void* scratch, int decode, dsb200_stream_t stream);
 int dsb200_paged_flash_latent(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride,
                               const void* cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                               int n_tokens, int heads, int rank, int block_size, int max_blocks_per_seq, int num_blocks,
@@ -168,7 +174,15 @@ int dsb200_paged_flash_window(const void* q, long long q_tok_stride, const void*
 /* Causal attention with soft-capped scores and a sink in the softmax, on the tensor-core kernels: weights exp(s_j) / (sink + sum_j exp(s_j)),
  * s_j = scale q . k_j, capped as softcap tanh(s_j / softcap) when softcap > 0 (two more MUFU operations per score).  q [n_tokens][hq][head_dim]
  * bf16 at q_tok_stride elements per token (a multiple of 8), kv_cache [num_blocks][2][block_size][hkv][head_dim] bf16; out rows at out_ld
- * elements per token (a multiple of 8).  decode != 0 selects the small-atom kernel (head_dim 128, q:kv head ratios dividing 16). */
+ * elements per token (a multiple of 8).  decode != 0 selects the small-atom kernel (head_dim 128, q:kv head ratios dividing 16).
+ * sink_logit (hq floats): learned sinks, exp(sink_logit[h]) joins head h's denominator; r1, r2 (hq floats each): the score of key j for the
+ * query at position i loses r1[h] ln(1 + r2[h] (i - j)); part > 0: a query sees only the keys of its own part of `part` positions.  Each may
+ * be absent (null / 0). */
+int dsb200_paged_flash_sink_ex(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld,
+                               const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int hq,
+                               int hkv, int head_dim, int block_size, int max_blocks_per_seq, int num_blocks, float scale,
+                               float softcap, float sink, const float* sink_logit, const float* r1, const float* r2,
+                               int part, int max_atoms, int n_splits, void* scratch, int decode, dsb200_stream_t stream);
 int dsb200_paged_flash_sink(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld,
                             const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int hq, int hkv,
                             int head_dim, int block_size, int max_blocks_per_seq, int num_blocks, float scale,
@@ -462,6 +476,17 @@ int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* 
  * out [R, N], all bf16 (dtype 0) or all fp32 (dtype 1), contiguous; fp32 accumulation.  expert_cumsum [E] int64 on the device. */
 int dsb200_moe_gemm_rows(const void* x, const void* w, void* out, const long long* expert_cumsum, int R, int N, int K,
                          int E, int dtype, dsb200_stream_t stream);
+/* x [rows, dim] fp32, in place: x <- s / sqrt(mean(s^2) + eps) * w with s = alpha x + y + y32 + bias; y [rows, dim] in y_dtype (0 = bf16,
+ * 1 = fp32), y32 [rows, dim] fp32, bias [dim] fp32 -- each may be null.  out (null, or [rows, dim] in out_dtype): the new x, rounded. */
+int dsb200_post_sum_norm(float* x, const void* y, int y_dtype, const float* y32, const float* bias, const float* w,
+                         void* out, int out_dtype, long long rows, int dim, float alpha, float eps,
+                         dsb200_stream_t stream);
+/* out [rows, F] = xIELU(u [rows, ld]): z > 0: coef[0] z^2 + z / 2; z <= 0: coef[1] (exp(z) - 1 - z) + z / 2; coef: two floats on the device. */
+int dsb200_xielu(const void* u, long long ld, void* out, long long rows, int F, const float* coef, int dtype,
+                 dsb200_stream_t stream);
+/* out[t, h dv + c] = a[h, t, c] * sigmoid(g[t, h]): a [H, n_tokens, dv] contiguous, g [n_tokens, g_ld] with one number per head. */
+int dsb200_gate_heads_scalar(const void* a, const void* g, long long g_ld, void* out, long long out_ld, int n_tokens,
+                             int H, int dv, int dtype, dsb200_stream_t stream);
 
 /* ---- csrc/ragged/ragged_ops.cu */
 int dsb200_kv_rotary_append(void* qkv, void* kv_cache, const int* tok_seq, const int* tok_pos, const int* block_table,
@@ -549,6 +574,14 @@ int dsb200_tied_gate_scan(const void* proj, long long ld, int q_col0, int f_col0
 int dsb200_head_norm_gate(const float* o, const float* w, int w_stride, const void* gate, long long gate_ld, void* out,
                           long long out_ld, int n_tokens, int H, int dv, float eps, float mult, int dtype,
                           dsb200_stream_t stream);
+long long dsb200_mingru_scratch_floats(int n_tokens, int n_seqs, int W);
+/* Minimal gated recurrence over every sequence's new tokens.  proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds the gate, candidate and output-gate
+ * pre-activations at columns z_col0 / x_col0 / g_col0 (W each); zb, xb fp32 [W]; state fp32 [slots, W]; out [T, out_ld] in proj's dtype.
+ * seq_desc [n_seqs, 4] = (first row, new tokens, tokens seen before, slot); tok_seq [T].  scratch: dsb200_mingru_scratch_floats floats, used
+ * when `pieces` != 0 (portions cut into pieces that are walked side by side); else one thread per (sequence, channel) walks its tokens. */
+int dsb200_mingru_scan(const void* proj, long long ld, int z_col0, int x_col0, int g_col0, const float* zb,
+                       const float* xb, const int* tok_seq, const int* seq_desc, float* state, void* out, long long out_ld,
+                       int n_tokens, int n_seqs, int W, int pieces, float* scratch, int dtype, dsb200_stream_t stream);
 
 /* ---- csrc/ragged/sink_attention_ops.cu */
 /* proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds per token the query heads [H d] at q_col0, the key heads [G d] at k_col0 and the value heads
@@ -572,6 +605,40 @@ int dsb200_sink_attention(const void* q, long long q_ld, const void* k_cache, lo
                           const int* block_table, int bt_stride, int block_size, void* out, long long out_ld, int n_tokens,
                           int H, int G, int d, int dv, float scale, float cap, float sink, int dtype,
                           dsb200_stream_t stream);
+/* `sink_attention` with learned sinks, a distance term, a mask by parts and free strides:
+ *   sink_logit [H] (or null): exp(sink_logit[h]) joins head h's denominator;   r1, r2 [H] (or both null): s_j -= r1[h] ln(1 + r2[h] (pos - j));
+ *   part > 0: only the keys of the query's own part of `part` positions (counted from position 0 of the sequence) are visible;
+ *   q[t * q_ld + h * q_head_stride + c], out[t * out_ld + h * out_head_stride + c]; a cached key / value head starts every k_row / v_row
+ *   elements of its token's row (one plane may serve as keys and as values: pass it twice, with d and dv entries read from a head's start). */
+int dsb200_sink_attention_ex(const void* q, long long q_ld, long long q_head_stride, const void* k_cache,
+                             long long k_block_stride, int k_row, const void* v_cache, long long v_block_stride, int v_row,
+                             const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride, int block_size,
+                             void* out, long long out_ld, long long out_head_stride, int n_tokens, int H, int G, int d,
+                             int dv, float scale, float cap, float sink, const float* sink_logit, const float* r1,
+                             const float* r2, int part, int dtype, dsb200_stream_t stream);
+/* Low-rank attention with one rotated key part shared by the heads.  proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds per token the H query heads
+ * (d plain entries, then dr entries to rotate) from q_col0 and the low-rank row (R entries, then dr entries to rotate) from kv_col0.  The
+ * query heads' rotated parts are rotated IN PLACE (first rot_dims of the dr entries; entry i pairs with entry i + rot_dims / 2; angle =
+ * pos * freq[i], freq: rot_dims / 2 doubles on the device); the first R entries of the low-rank row are RMS-normed with wkv [R] and, with the
+ * rotated last dr entries behind them, written to the token's row of cache [blocks, block_size, row_w] (zeros from R + dr on). */
+int dsb200_latent_rotary_append(void* proj, long long ld, int q_col0, int kv_col0, const float* wkv, const double* freq,
+                                const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
+                                int block_size, void* cache, int row_w, int n_tokens, int H, int d, int dr, int R,
+                                int rot_dims, float eps, int dtype, dsb200_stream_t stream);
+/* Attention inputs behind a short causal convolution.  proj [T, ld] holds from col0 on the query heads [H d], the key heads [G d] and the value
+ * heads [G dv] of every token; bias (fp32, that many entries, or null) is added to every row before the convolution with conv_w (fp32
+ * [channels, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence's start).  state [slots, taps - 1, channels]: the last
+ * rows of the sequence's earlier steps, WITHOUT the bias (update it afterwards with dsb200_conv_state_update).  Query / key heads: RMS norm over
+ * d with wq / wk [d] shared by the heads -> q_out [T, q_ld] (head h at h * q_row) / the key plane.  Value heads: v_own (null, or [T, G dv])
+ * receives the convolved values; with v_other ([T, G dv]) and mix (one float on the device) the cached value is (1 - mix) v + mix v_other.
+ * Heads are padded with zeros to q_row / k_row / v_row entries. */
+int dsb200_conv_head_norm_append(const void* proj, long long ld, int col0, const float* bias, const float* conv_w,
+                                 const float* wq, const float* wk, const void* state, const int* seq_desc,
+                                 const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
+                                 int block_size, void* k_cache, long long k_block_stride, void* v_cache,
+                                 long long v_block_stride, void* q_out, long long q_ld, const void* v_other,
+                                 const float* mix, void* v_own, int n_tokens, int H, int G, int d, int dv, int taps,
+                                 float eps, int q_row, int k_row, int v_row, int dtype, dsb200_stream_t stream);
 
 /* ---- csrc/random_ltd/token_ops.cu */
 /* idx: int32 [rows, reserved] of unique positions in [0, seq); sorted ascending in place, row by row. */
