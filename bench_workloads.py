@@ -1086,7 +1086,7 @@ def _midulorn_kernel_table(torch, peaks, W, H, d, hkv, E, top, ff, T, ctx, n_dec
         qo = torch.empty(Tn, H * d, device=dev, dtype=bf)
         planes = K.cache_planes(kv)
         C = (H + 2 * hkv) * d
-        cw, cb, mix = torch.randn(C, MIDULORN_TAPS, device=dev), torch.randn(C, device=dev), torch.full((1, ), 0.3, device=dev)
+        cw, cb, mix = torch.randn(MIDULORN_TAPS, C, device=dev), torch.randn(C, device=dev), torch.full((1, ), 0.3, device=dev)
         cstate = torch.zeros(n_seq, MIDULORN_TAPS - 1, C, device=dev, dtype=bf)
         vsrc = torch.randn(Tn, hkv * d, device=dev).to(bf)
 

@@ -1200,38 +1200,58 @@ __global__ void post_sum_norm_kernel(float* __restrict__ x, const TY* __restrict
   }
 }
 
+// exp(z) - 1 - z for z <= 0.  A bf16 result takes the fast exponential: its absolute error (~1e-7) is below bf16's rounding of the z / 2 the
+// term is added to; an fp32 result takes expm1f.
+template <typename T>
+__device__ __forceinline__ float xielu_tail(float z);
+template <>
+__device__ __forceinline__ float xielu_tail<float>(float z) { return expm1f(z) - z; }
+template <>
+__device__ __forceinline__ float xielu_tail<bf16>(float z) { return (__expf(z) - 1.f) - z; }
+template <typename T>
+__device__ __forceinline__ float xielu_one(float z, float a, float b) {
+  return z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, xielu_tail<T>(z), 0.5f * z);
+}
+
 template <typename T>
 __global__ void xielu_kernel(const T* __restrict__ u, long long ld, T* __restrict__ out, long long rows, int F, const float* __restrict__ coef) {
   const float a = coef[0], b = coef[1];
   const long long n = rows * F;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float z = to_f(u[(i / F) * ld + (i % F)]);
-    out[i] = from_f<T>(z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z));
-  }
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = from_f<T>(xielu_one<T>(to_f(u[(i / F) * ld + (i % F)]), a, b));
 }
 template <typename T>
 __global__ void xielu_vec_kernel(const T* __restrict__ u, T* __restrict__ out, long long n4, const float* __restrict__ coef) {
   const float a = coef[0], b = coef[1];
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float4 z = load4(u + 4 * i);
-    z.x = z.x > 0.f ? fmaf(a * z.x, z.x, 0.5f * z.x) : fmaf(b, expm1f(z.x) - z.x, 0.5f * z.x);
-    z.y = z.y > 0.f ? fmaf(a * z.y, z.y, 0.5f * z.y) : fmaf(b, expm1f(z.y) - z.y, 0.5f * z.y);
-    z.z = z.z > 0.f ? fmaf(a * z.z, z.z, 0.5f * z.z) : fmaf(b, expm1f(z.z) - z.z, 0.5f * z.z);
-    z.w = z.w > 0.f ? fmaf(a * z.w, z.w, 0.5f * z.w) : fmaf(b, expm1f(z.w) - z.w, 0.5f * z.w);
+    z.x = xielu_one<T>(z.x, a, b);
+    z.y = xielu_one<T>(z.y, a, b);
+    z.z = xielu_one<T>(z.z, a, b);
+    z.w = xielu_one<T>(z.w, a, b);
     store4(out + 4 * i, z);
   }
 }
 
-template <typename T>
+// VEC: dv % 4 == 0, out_ld % 4 == 0 and 16-byte aligned a / out: four values per thread.
+template <typename T, bool VEC>
 __global__ void gate_heads_scalar_kernel(const T* __restrict__ a, const T* __restrict__ g, long long g_ld, T* __restrict__ out, long long out_ld,
                                          int n_tokens, int H, int dv) {
+  constexpr int V = VEC ? 4 : 1;
   const int row = H * dv;
-  const long long n = static_cast<long long>(n_tokens) * row;
-  for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < n; e += static_cast<long long>(gridDim.x) * blockDim.x) {
+  const long long n = static_cast<long long>(n_tokens) * row / V;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * V;
     const long long t = e / row;
     const int rem = static_cast<int>(e % row), h = rem / dv, c = rem % dv;
     const float gate = 1.f / (1.f + expf(-to_f(g[t * g_ld + h])));
-    out[t * out_ld + rem] = from_f<T>(to_f(a[(static_cast<long long>(h) * n_tokens + t) * dv + c]) * gate);
+    const T* src = a + (static_cast<long long>(h) * n_tokens + t) * dv + c;
+    if constexpr (VEC) {
+      const float4 v = load4(src);
+      store4(out + t * out_ld + rem, make_float4(v.x * gate, v.y * gate, v.z * gate, v.w * gate));
+    } else {
+      out[t * out_ld + rem] = from_f<T>(to_f(*src) * gate);
+    }
   }
 }
 
@@ -1282,8 +1302,13 @@ DSB_EXPORT int dsb200_gate_heads_scalar(const void* a, const void* g, long long 
   const long long n = static_cast<long long>(n_tokens) * H * dv;
   if (n == 0) return DSB_OK;
   DSB_REQUIRE(out_ld >= static_cast<long long>(H) * dv && g_ld >= H, "gate_heads_scalar: strides %lld / %lld", out_ld, g_ld);
-  if (dtype == 0) gate_heads_scalar_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)a, (const bf16*)g, g_ld, (bf16*)out, out_ld, n_tokens, H, dv);
-  else gate_heads_scalar_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)a, (const float*)g, g_ld, (float*)out, out_ld, n_tokens, H, dv);
+  const bool vec = dv % 4 == 0 && out_ld % 4 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+#define LAUNCH(T, V) gate_heads_scalar_kernel<T, V><<<grid_for(n / (V ? 4 : 1), 256), 256, 0, stream>>>((const T*)a, (const T*)g, g_ld, (T*)out, out_ld, n_tokens, H, dv)
+  if (dtype == 0 && vec) LAUNCH(bf16, true);
+  else if (dtype == 0) LAUNCH(bf16, false);
+  else if (vec) LAUNCH(float, true);
+  else LAUNCH(float, false);
+#undef LAUNCH
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

@@ -1095,101 +1095,199 @@ namespace recur {
 
 constexpr int MG_PIECE = 32;
 
-struct MinGruIn {
-  float a, b, g;
+struct alignas(8) mg_bf16x4 {
+  __nv_bfloat162 a, b;
 };
-template <typename T>
-__device__ __forceinline__ MinGruIn mingru_load(const T* __restrict__ row, int z0, int x0, int g0, int c, float bz, float bx) {
-  const float z = sigmoidf_(to_f(row[z0 + c]) + bz);
-  const float u = to_f(row[x0 + c]) + bx;
-  MinGruIn r;
-  r.a = 1.f - z;
-  r.b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
-  r.g = to_f(row[g0 + c]);
-  return r;
+// V neighbouring channels per thread (V = 4: every offset, stride and the width are multiples of 4 and the rows 16-byte aligned)
+template <int V>
+__device__ __forceinline__ void mg_load(const float* p, float* o) {
+  if constexpr (V == 4) { const float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+  else o[0] = *p;
+}
+template <int V>
+__device__ __forceinline__ void mg_load(const bf16* p, float* o) {
+  if constexpr (V == 4) {
+    const mg_bf16x4 v = *reinterpret_cast<const mg_bf16x4*>(p);
+    const float2 lo = __bfloat1622float2(v.a), hi = __bfloat1622float2(v.b);
+    o[0] = lo.x; o[1] = lo.y; o[2] = hi.x; o[3] = hi.y;
+  } else o[0] = __bfloat162float(*p);
+}
+template <int V>
+__device__ __forceinline__ void mg_store(float* p, const float* v) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else *p = v[0];
+}
+template <int V>
+__device__ __forceinline__ void mg_store(bf16* p, const float* v) {
+  if constexpr (V == 4) {
+    mg_bf16x4 o;
+    o.a = __floats2bfloat162_rn(v[0], v[1]);
+    o.b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<mg_bf16x4*>(p) = o;
+  } else *p = __float2bfloat16_rn(v[0]);
+}
+// the affine map of one token, S -> a S + b, from its gate and candidate pre-activations
+template <int V>
+__device__ __forceinline__ void mg_map(const float* pz, const float* px, const float* bz, const float* bx, float* a, float* b) {
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    const float z = sigmoidf_(pz[e] + bz[e]);
+    const float u = px[e] + bx[e];
+    a[e] = 1.f - z;
+    b[e] = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+  }
+}
+template <typename T, int V>
+__device__ __forceinline__ void mg_step(const float* pz, const float* px, const float* pg, const float* bz, const float* bx, float* S,
+                                        T* __restrict__ out) {
+  float a[V], b[V], o[V];
+  mg_map<V>(pz, px, bz, bx, a, b);
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    S[e] = fmaf(a[e], S[e], b[e]);
+    o[e] = S[e] * siluf_(pg[e]);
+  }
+  mg_store<V>(out, o);
 }
 
-template <typename T>
+constexpr int MG_AHEAD = 4;  // tokens whose rows are loaded before the first of them is used: the walk is bound by load latency otherwise
+
+template <typename T, int V>
 __global__ void mingru_scan_kernel(const T* __restrict__ proj, long long ld, int z0, int x0, int g0, const float* __restrict__ zb,
                                    const float* __restrict__ xb, const int4* __restrict__ seq_desc, float* __restrict__ state,
                                    T* __restrict__ out, long long out_ld, int W) {
   const int4 sd = seq_desc[blockIdx.y];
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (c >= W) return;
   float* st = state + static_cast<size_t>(sd.w) * W + c;
-  float S = sd.z > 0 ? *st : 0.f;  // a sequence at position 0 starts from zero whatever the slot held
-  const float bz = zb[c], bx = xb[c];
-  const T* row = proj + static_cast<long long>(sd.x) * ld;
-  T* o = out + static_cast<long long>(sd.x) * out_ld + c;
-  for (int i = 0; i < sd.y; ++i, row += ld, o += out_ld) {
-    const MinGruIn in = mingru_load(row, z0, x0, g0, c, bz, bx);
-    S = fmaf(in.a, S, in.b);
-    *o = from_f<T>(S * siluf_(in.g));
+  float S[V], bz[V], bx[V];
+  mg_load<V>(st, S);
+  if (sd.z == 0) {  // a sequence at position 0 starts from zero whatever the slot held
+#pragma unroll
+    for (int e = 0; e < V; ++e) S[e] = 0.f;
   }
-  *st = S;
+  mg_load<V>(zb + c, bz);
+  mg_load<V>(xb + c, bx);
+  const T* row = proj + static_cast<long long>(sd.x) * ld + c;
+  T* o = out + static_cast<long long>(sd.x) * out_ld + c;
+  for (int i = 0; i < sd.y; i += MG_AHEAD) {
+    float pz[MG_AHEAD][V], px[MG_AHEAD][V], pg[MG_AHEAD][V];
+#pragma unroll
+    for (int u = 0; u < MG_AHEAD; ++u)
+      if (i + u < sd.y) {
+        const T* r = row + static_cast<long long>(i + u) * ld;
+        mg_load<V>(r + z0, pz[u]);
+        mg_load<V>(r + x0, px[u]);
+        mg_load<V>(r + g0, pg[u]);
+      }
+#pragma unroll
+    for (int u = 0; u < MG_AHEAD; ++u)
+      if (i + u < sd.y) mg_step<T, V>(pz[u], px[u], pg[u], bz, bx, S, o + static_cast<long long>(i + u) * out_ld);
+  }
+  mg_store<V>(st, S);
 }
 
-// start[t]: -1 inside a sequence, else the index of the sequence whose first new token is row t.
-template <typename T>
+template <typename T, int V>
 __global__ void mingru_pieces_kernel(const T* __restrict__ proj, long long ld, int z0, int x0, const float* __restrict__ zb,
                                      const float* __restrict__ xb, const int* __restrict__ tok_seq, const int4* __restrict__ seq_desc,
                                      const float* __restrict__ state, float* __restrict__ init, float* __restrict__ pa, float* __restrict__ pb,
                                      int n_tokens, int W) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (c >= W) return;
   const int p = blockIdx.y, t0 = p * MG_PIECE, t1 = min(n_tokens, t0 + MG_PIECE);
-  const float bz = zb[c], bx = xb[c];
-  float A = 1.f, B = 0.f;
-  for (int t = t0; t < t1; ++t) {
-    const int s = tok_seq[t];
-    const int4 sd = seq_desc[s];
-    if (t == sd.x) {  // the sequence's own state replaces what came before
-      const float S0 = sd.z > 0 ? state[static_cast<size_t>(sd.w) * W + c] : 0.f;
-      init[static_cast<size_t>(s) * W + c] = S0;
-      A = 0.f;
-      B = S0;
-    }
-    const T* row = proj + static_cast<long long>(t) * ld;
-    const float z = sigmoidf_(to_f(row[z0 + c]) + bz);
-    const float u = to_f(row[x0 + c]) + bx;
-    const float a = 1.f - z, b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
-    A *= a;
-    B = fmaf(a, B, b);
+  float bz[V], bx[V], A[V], B[V];
+  mg_load<V>(zb + c, bz);
+  mg_load<V>(xb + c, bx);
+#pragma unroll
+  for (int e = 0; e < V; ++e) { A[e] = 1.f; B[e] = 0.f; }
+  for (int t = t0; t < t1; t += MG_AHEAD) {
+    float pz[MG_AHEAD][V], px[MG_AHEAD][V];
+    int4 sd[MG_AHEAD];
+    int sq[MG_AHEAD];
+#pragma unroll
+    for (int u = 0; u < MG_AHEAD; ++u)
+      if (t + u < t1) {
+        const T* r = proj + static_cast<long long>(t + u) * ld + c;
+        mg_load<V>(r + z0, pz[u]);
+        mg_load<V>(r + x0, px[u]);
+        sq[u] = tok_seq[t + u];
+        sd[u] = seq_desc[sq[u]];
+      }
+#pragma unroll
+    for (int u = 0; u < MG_AHEAD; ++u)
+      if (t + u < t1) {
+        if (t + u == sd[u].x) {  // the sequence's own state replaces what came before
+          mg_load<V>(state + static_cast<size_t>(sd[u].w) * W + c, B);
+#pragma unroll
+          for (int e = 0; e < V; ++e) { A[e] = 0.f; B[e] = sd[u].z > 0 ? B[e] : 0.f; }
+          mg_store<V>(init + static_cast<size_t>(sq[u]) * W + c, B);
+        }
+        float a[V], b[V];
+        mg_map<V>(pz[u], px[u], bz, bx, a, b);
+#pragma unroll
+        for (int e = 0; e < V; ++e) { A[e] *= a[e]; B[e] = fmaf(a[e], B[e], b[e]); }
+      }
   }
-  pa[static_cast<size_t>(p) * W + c] = A;
-  pb[static_cast<size_t>(p) * W + c] = B;
+  mg_store<V>(pa + static_cast<size_t>(p) * W + c, A);
+  mg_store<V>(pb + static_cast<size_t>(p) * W + c, B);
 }
 
 __global__ void mingru_carry_kernel(const float* __restrict__ pa, float* __restrict__ pb, int n_pieces, int W) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= W) return;
+  constexpr int AHEAD = 8;  // the maps of that many pieces are loaded before the first is applied (the walk itself is a chain)
   float S = 0.f;  // row 0 starts a sequence, so the first piece has A = 0
-  for (int p = 0; p < n_pieces; ++p) {
-    const size_t i = static_cast<size_t>(p) * W + c;
-    const float A = pa[i], B = pb[i];
-    pb[i] = S;  // the state in front of piece p
-    S = fmaf(A, S, B);
+  for (int p = 0; p < n_pieces; p += AHEAD) {
+    float A[AHEAD], B[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u)
+      if (p + u < n_pieces) {
+        const size_t i = static_cast<size_t>(p + u) * W + c;
+        A[u] = pa[i];
+        B[u] = pb[i];
+      }
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u)
+      if (p + u < n_pieces) {
+        pb[static_cast<size_t>(p + u) * W + c] = S;  // the state in front of piece p + u
+        S = fmaf(A[u], S, B[u]);
+      }
   }
 }
 
-template <typename T>
+template <typename T, int V>
 __global__ void mingru_apply_kernel(const T* __restrict__ proj, long long ld, int z0, int x0, int g0, const float* __restrict__ zb,
                                     const float* __restrict__ xb, const int* __restrict__ tok_seq, const int4* __restrict__ seq_desc,
                                     float* __restrict__ state, const float* __restrict__ init, const float* __restrict__ carry,
                                     T* __restrict__ out, long long out_ld, int n_tokens, int W) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (c >= W) return;
   const int p = blockIdx.y, t0 = p * MG_PIECE, t1 = min(n_tokens, t0 + MG_PIECE);
-  const float bz = zb[c], bx = xb[c];
-  float S = carry[static_cast<size_t>(p) * W + c];
-  for (int t = t0; t < t1; ++t) {
-    const int s = tok_seq[t];
-    const int4 sd = seq_desc[s];
-    if (t == sd.x) S = init[static_cast<size_t>(s) * W + c];
-    const MinGruIn in = mingru_load(proj + static_cast<long long>(t) * ld, z0, x0, g0, c, bz, bx);
-    S = fmaf(in.a, S, in.b);
-    out[static_cast<long long>(t) * out_ld + c] = from_f<T>(S * siluf_(in.g));
-    if (t == sd.x + sd.y - 1) state[static_cast<size_t>(sd.w) * W + c] = S;
+  float bz[V], bx[V], S[V];
+  mg_load<V>(zb + c, bz);
+  mg_load<V>(xb + c, bx);
+  mg_load<V>(carry + static_cast<size_t>(p) * W + c, S);
+  for (int t = t0; t < t1; t += MG_AHEAD) {
+    float pz[MG_AHEAD][V], px[MG_AHEAD][V], pg[MG_AHEAD][V];
+    int4 sd[MG_AHEAD];
+    int sq[MG_AHEAD];
+#pragma unroll
+    for (int u = 0; u < MG_AHEAD; ++u)
+      if (t + u < t1) {
+        const T* r = proj + static_cast<long long>(t + u) * ld + c;
+        mg_load<V>(r + z0, pz[u]);
+        mg_load<V>(r + x0, px[u]);
+        mg_load<V>(r + g0, pg[u]);
+        sq[u] = tok_seq[t + u];
+        sd[u] = seq_desc[sq[u]];
+      }
+#pragma unroll
+    for (int u = 0; u < MG_AHEAD; ++u)
+      if (t + u < t1) {
+        if (t + u == sd[u].x) mg_load<V>(init + static_cast<size_t>(sq[u]) * W + c, S);
+        mg_step<T, V>(pz[u], px[u], pg[u], bz, bx, S, out + static_cast<long long>(t + u) * out_ld + c);
+        if (t + u == sd[u].x + sd[u].y - 1) mg_store<V>(state + static_cast<size_t>(sd[u].w) * W + c, S);
+      }
   }
 }
 
@@ -1211,13 +1309,19 @@ DSB_EXPORT int dsb200_mingru_scan(const void* proj, long long ld, int z_col0, in
   if (n_tokens == 0 || n_seqs == 0) return DSB_OK;
   DSB_REQUIRE(W >= 1 && out_ld >= W && zb != nullptr && xb != nullptr && state != nullptr, "mingru_scan: width %d, output stride %lld", W, out_ld);
   const int threads = 128;
-  const unsigned gx = static_cast<unsigned>((W + threads - 1) / threads);
+  auto mult4 = [](long long v) { return v % 4 == 0; };
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = mult4(W) && mult4(ld) && mult4(out_ld) && mult4(z_col0) && mult4(x_col0) && mult4(g_col0) && al16(proj) && al16(out) && al16(zb) && al16(xb) &&
+                   al16(state) && al16(scratch);
+  const int per = vec ? 4 : 1;
+  const unsigned gx = static_cast<unsigned>((W / per + threads - 1) / threads);
+  const unsigned gx1 = static_cast<unsigned>((W + threads - 1) / threads);
   if (!pieces) {
     const dim3 grid(gx, n_seqs);
-    if (dtype == 0)
-      mingru_scan_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (bf16*)out, out_ld, W);
-    else
-      mingru_scan_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (float*)out, out_ld, W);
+    if (dtype == 0 && vec) mingru_scan_kernel<bf16, 4><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (bf16*)out, out_ld, W);
+    else if (dtype == 0) mingru_scan_kernel<bf16, 1><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (bf16*)out, out_ld, W);
+    else if (vec) mingru_scan_kernel<float, 4><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (float*)out, out_ld, W);
+    else mingru_scan_kernel<float, 1><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, (const int4*)seq_desc, state, (float*)out, out_ld, W);
     DSB_CHECK_CUDA(cudaGetLastError());
     return DSB_OK;
   }
@@ -1227,17 +1331,15 @@ DSB_EXPORT int dsb200_mingru_scan(const void* proj, long long ld, int z_col0, in
   float* pb = pa + static_cast<size_t>(np) * W;
   float* init = pb + static_cast<size_t>(np) * W;
   const dim3 grid(gx, np);
-  if (dtype == 0)
-    mingru_pieces_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
-  else
-    mingru_pieces_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
-  mingru_carry_kernel<<<gx, threads, 0, stream>>>(pa, pb, np, W);
-  if (dtype == 0)
-    mingru_apply_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb,
-                                                           (bf16*)out, out_ld, n_tokens, W);
-  else
-    mingru_apply_kernel<float><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb,
-                                                            (float*)out, out_ld, n_tokens, W);
+  if (dtype == 0 && vec) mingru_pieces_kernel<bf16, 4><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
+  else if (dtype == 0) mingru_pieces_kernel<bf16, 1><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
+  else if (vec) mingru_pieces_kernel<float, 4><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
+  else mingru_pieces_kernel<float, 1><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pa, pb, n_tokens, W);
+  mingru_carry_kernel<<<gx1, threads, 0, stream>>>(pa, pb, np, W);
+  if (dtype == 0 && vec) mingru_apply_kernel<bf16, 4><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb, (bf16*)out, out_ld, n_tokens, W);
+  else if (dtype == 0) mingru_apply_kernel<bf16, 1><<<grid, threads, 0, stream>>>((const bf16*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb, (bf16*)out, out_ld, n_tokens, W);
+  else if (vec) mingru_apply_kernel<float, 4><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb, (float*)out, out_ld, n_tokens, W);
+  else mingru_apply_kernel<float, 1><<<grid, threads, 0, stream>>>((const float*)proj, ld, z_col0, x_col0, g_col0, zb, xb, tok_seq, (const int4*)seq_desc, state, init, pb, (float*)out, out_ld, n_tokens, W);
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

@@ -258,72 +258,197 @@ __global__ void latent_rotary_append_kernel(T* __restrict__ proj, long long ld, 
   for (int c = R + dr + lane; c < row_w; c += 32) dst[c] = from_f<T>(0.f);  // rows padded to a width the tensor-core kernels take
 }
 
-// One warp per (token, head slot): the H query heads, then the G key heads, then the G value heads of the token.  Every channel first passes
-// a short causal convolution over the sequence (bias added to every real row; rows before this step's come from the state, rows before the
-// sequence are zeros); query / key heads then get their RMS norm, value heads are mixed with another layer's values of the same token.
-template <typename T>
-__global__ void conv_head_norm_append_kernel(const T* __restrict__ proj, long long ld, int col0, const float* __restrict__ bias,
-                                             const float* __restrict__ conv_w, const float* __restrict__ wq, const float* __restrict__ wk,
-                                             const T* __restrict__ state, const int4* __restrict__ seq_desc, const int* __restrict__ tok_seq,
-                                             const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride, int block_size,
-                                             T* __restrict__ k_cache, long long k_block_stride, T* __restrict__ v_cache, long long v_block_stride,
-                                             T* __restrict__ q_out, long long q_ld, const T* __restrict__ v_other, const float* __restrict__ mix,
-                                             T* __restrict__ v_own, int n_tokens, int H, int G, int d, int dv, int taps, float eps, int q_row,
-                                             int k_row, int v_row) {
+struct alignas(8) bf16x4 {
+  __nv_bfloat162 a, b;
+};
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const bf16x4 v = *reinterpret_cast<const bf16x4*>(p);
+  const float2 lo = __bfloat1622float2(v.a), hi = __bfloat1622float2(v.b);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  bf16x4 o;
+  o.a = __floats2bfloat162_rn(v.x, v.y);
+  o.b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<bf16x4*>(p) = o;
+}
+
+// One warp per (token, SL consecutive head slots): the H query heads, then the G key heads, then the G value heads of the token.  Every
+// channel first passes a short causal convolution over the sequence (bias added to every real row; rows before this step's come from the
+// state, rows before the sequence are zeros); query / key heads then get their RMS norm, value heads are mixed with another layer's values of
+// the same token.  A lane owns VEC neighbouring channels at a time (VEC = 4: every size, offset and stride is a multiple of 4 and the rows
+// are 16-byte aligned).  SL = 1: heads of any size; the convolved values of up to CH_REGS channels per lane stay in registers between the
+// statistic and the scaling, what a wider head has beyond them is convolved a second time.  SL > 1 (heads of at most 32 VEC entries): the
+// loads of all SL slots are issued before the first statistic is formed, and the token's metadata is read once for all of them -- the kernel
+// is bound by the latency of its dependent loads, not by their volume.
+constexpr int CH_REGS = 8;
+template <typename T, int VEC, int SL>
+__global__ void __launch_bounds__(256, 4)
+conv_head_norm_append_kernel(const T* __restrict__ proj, long long ld, int col0, const float* __restrict__ bias, const float* __restrict__ conv_w,
+                             const float* __restrict__ wq, const float* __restrict__ wk, const T* __restrict__ state,
+                             const int4* __restrict__ seq_desc, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                             const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ k_cache, long long k_block_stride,
+                             T* __restrict__ v_cache, long long v_block_stride, T* __restrict__ q_out, long long q_ld, const T* __restrict__ v_other,
+                             const float* __restrict__ mix, T* __restrict__ v_own, int n_tokens, int H, int G, int d, int dv, int taps, float eps,
+                             int q_row, int k_row, int v_row) {
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int per_tok = H + 2 * G;
-  if (gw >= n_tokens * per_tok) return;
-  const int t = gw / per_tok, slot = gw % per_tok;
+  const int per_tok = H + 2 * G, groups = (per_tok + SL - 1) / SL;
+  if (gw >= n_tokens * groups) return;
+  const int t = gw / groups, slot0 = (gw % groups) * SL;
   const int seq = tok_seq[t], pos = tok_pos[t];
   const int4 sd = seq_desc[seq];
   const int i = t - sd.x;  // index among the sequence's new tokens
   const int C = (H + G) * d + G * dv;  // convolved channels: q | k | v, as they lie in proj from col0 on and in the state rows
-  const bool is_q = slot < H, is_v = slot >= H + G;
-  const int head = is_q ? slot : (is_v ? slot - H - G : slot - H);
-  const int n = is_v ? dv : d;
-  const int ch0 = is_q ? head * d : (is_v ? (H + G) * d + head * dv : H * d + head * d);
   const T* st = state ? state + static_cast<size_t>(sd.w) * (taps - 1) * C : nullptr;
-  long long cache_row = 0;
-  if (!is_q) cache_row = block_table[static_cast<size_t>(seq) * bt_stride + pos / block_size];
+  const long long cache_row = block_table[static_cast<size_t>(seq) * bt_stride + pos / block_size];
   const int in_block = pos % block_size;
-  T* dst = is_q ? q_out + static_cast<long long>(t) * q_ld + head * q_row
-                : (is_v ? v_cache + cache_row * v_block_stride + (static_cast<long long>(in_block) * G + head) * v_row
-                        : k_cache + cache_row * k_block_stride + (static_cast<long long>(in_block) * G + head) * k_row);
-  const int width = is_q ? q_row : (is_v ? v_row : k_row);
-  // the head's channels: up to 8 per lane in registers, the rest recomputed (heads above 256 entries)
-  float ss = 0.f;
-  for (int pass = 0; pass < 2; ++pass) {
-    float inv = 1.f;
-    if (pass == 1) {
-      if (is_v) break;
-      ss = warp_sum(ss);
-      inv = 1.f / sqrtf(ss / static_cast<float>(n) + eps);
-    }
-    for (int c = lane; c < n; c += 32) {
-      const int ch = ch0 + c;
+  // rows the taps read: tap j reads the token taps - 1 - j positions back -- a row of this step, a row of the state, or nothing
+  const int j0 = max(0, taps - 1 - pos);           // taps before j0 lie before the sequence's start
+  const int js = min(taps, max(j0, taps - 1 - i));  // taps j0 .. js - 1 read the state, taps js .. read rows of this step
+  const T* own = proj + static_cast<long long>(sd.x + i - (taps - 1)) * ld + col0;  // + j * ld: the row of tap j (j >= js)
+  const T* old = st ? st + static_cast<long long>(i) * C : nullptr;               // + j * C: the state row of tap j (j < js)
+
+  struct Slot {
+    bool is_q, is_v;
+    int head, n, ch0, width;
+    T* dst;
+  };
+  auto slot_of = [&](int slot) {
+    Slot o;
+    o.is_q = slot < H;
+    o.is_v = slot >= H + G;
+    o.head = o.is_q ? slot : (o.is_v ? slot - H - G : slot - H);
+    o.n = o.is_v ? dv : d;
+    o.ch0 = o.is_q ? o.head * d : (o.is_v ? (H + G) * d + o.head * dv : H * d + o.head * d);
+    o.width = o.is_q ? q_row : (o.is_v ? v_row : k_row);
+    o.dst = o.is_q ? q_out + static_cast<long long>(t) * q_ld + o.head * q_row
+                   : (o.is_v ? v_cache + cache_row * v_block_stride + (static_cast<long long>(in_block) * G + o.head) * v_row
+                             : k_cache + cache_row * k_block_stride + (static_cast<long long>(in_block) * G + o.head) * k_row);
+    return o;
+  };
+  auto conv = [&](int ch, float* y) {  // VEC channels from ch on
+    if constexpr (VEC == 4) {
+      const float4 b = bias ? load4(bias + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = j0; j < taps; ++j) {
+        const float4 u = j < js ? load4(old + static_cast<long long>(j) * C + ch) : load4(own + static_cast<long long>(j) * ld + ch);
+        const float4 w = load4(conv_w + static_cast<size_t>(j) * C + ch);  // [taps, channels]: the lanes of a warp read one stretch
+        a.x = fmaf(w.x, u.x + b.x, a.x);
+        a.y = fmaf(w.y, u.y + b.y, a.y);
+        a.z = fmaf(w.z, u.z + b.z, a.z);
+        a.w = fmaf(w.w, u.w + b.w, a.w);
+      }
+      y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w;
+    } else {
       const float b = bias ? bias[ch] : 0.f;
-      float y = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int ii = i - (taps - 1) + j;  // index among the new tokens of the row this tap reads
-        float u;
-        if (ii >= 0) u = to_f(proj[static_cast<long long>(sd.x + ii) * ld + col0 + ch]) + b;
-        else if (pos - i + ii >= 0) u = to_f(st[static_cast<size_t>(taps - 1 + ii) * C + ch]) + b;  // a row of an earlier step
-        else continue;  // before the sequence's start
-        y = fmaf(conv_w[static_cast<size_t>(ch) * taps + j], u, y);
+      float a = 0.f;
+      for (int j = j0; j < taps; ++j) {
+        const float u = to_f(j < js ? old[static_cast<long long>(j) * C + ch] : own[static_cast<long long>(j) * ld + ch]);
+        a = fmaf(conv_w[static_cast<size_t>(j) * C + ch], u + b, a);
       }
-      if (is_v) {
-        const size_t vi = static_cast<size_t>(t) * G * dv + head * dv + c;
-        if (v_own) v_own[vi] = from_f<T>(y);
-        if (v_other) { const float lam = mix[0]; y = (1.f - lam) * y + lam * to_f(v_other[vi]); }
-        dst[c] = from_f<T>(y);
-      } else if (pass == 0) {
-        ss += y * y;
+      y[0] = a;
+    }
+  };
+  auto emit = [&](const Slot& S, int c, const float* y, float inv) {  // scale (queries / keys) or mix (values) and store VEC channels from c on
+    float o[VEC];
+    if (S.is_v) {
+      const size_t vi = static_cast<size_t>(t) * G * dv + S.head * dv + c;
+      if (v_own) {
+        if constexpr (VEC == 4) store4(v_own + vi, make_float4(y[0], y[1], y[2], y[3]));
+        else v_own[vi] = from_f<T>(y[0]);
+      }
+      if (v_other) {
+        const float lam = mix[0];
+        if constexpr (VEC == 4) {
+          const float4 w = load4(v_other + vi);
+          o[0] = (1.f - lam) * y[0] + lam * w.x; o[1] = (1.f - lam) * y[1] + lam * w.y; o[2] = (1.f - lam) * y[2] + lam * w.z; o[3] = (1.f - lam) * y[3] + lam * w.w;
+        } else {
+          o[0] = (1.f - lam) * y[0] + lam * to_f(v_other[vi]);
+        }
       } else {
-        dst[c] = from_f<T>(y * inv * (is_q ? wq[c] : wk[c]));
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = y[e];
+      }
+    } else {
+      const float* w = S.is_q ? wq : wk;
+      if constexpr (VEC == 4) {
+        const float4 g = load4(w + c);
+        o[0] = y[0] * inv * g.x; o[1] = y[1] * inv * g.y; o[2] = y[2] * inv * g.z; o[3] = y[3] * inv * g.w;
+      } else {
+        o[0] = y[0] * inv * w[c];
       }
     }
+    if constexpr (VEC == 4) store4(S.dst + c, make_float4(o[0], o[1], o[2], o[3]));
+    else S.dst[c] = from_f<T>(o[0]);
+  };
+
+  if constexpr (SL > 1) {
+    const int c = lane * VEC;
+    float held[SL][VEC];
+#pragma unroll
+    for (int s = 0; s < SL; ++s) {
+      if (slot0 + s < per_tok) {
+        const Slot S = slot_of(slot0 + s);
+        if (c < S.n) conv(S.ch0 + c, held[s]);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < SL; ++s) {
+      if (slot0 + s < per_tok) {  // uniform over the warp
+        const Slot S = slot_of(slot0 + s);
+        float ss = 0.f;
+        if (c < S.n) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) ss += held[s][e] * held[s][e];
+        }
+        float inv = 1.f;
+        if (!S.is_v) {
+          ss = warp_sum(ss);
+          inv = 1.f / sqrtf(ss / static_cast<float>(S.n) + eps);
+        }
+        if (c < S.n) emit(S, c, held[s], inv);
+        for (int x = S.n + lane; x < S.width; x += 32) S.dst[x] = from_f<T>(0.f);  // padding: adds nothing to a score or an output
+      }
+    }
+  } else {
+    const Slot S = slot_of(slot0);
+    constexpr int GROUPS = CH_REGS / VEC;
+    float held[CH_REGS];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < GROUPS; ++k) {
+      const int c = (lane + 32 * k) * VEC;
+      if (c < S.n) {
+        conv(S.ch0 + c, held + k * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss += held[k * VEC + e] * held[k * VEC + e];
+      }
+    }
+    for (int c = (lane + 32 * GROUPS) * VEC; c < S.n; c += 32 * VEC) {  // heads wider than the registers hold
+      float y[VEC];
+      conv(S.ch0 + c, y);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss += y[e] * y[e];
+    }
+    float inv = 1.f;
+    if (!S.is_v) {
+      ss = warp_sum(ss);
+      inv = 1.f / sqrtf(ss / static_cast<float>(S.n) + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < GROUPS; ++k) {
+      const int c = (lane + 32 * k) * VEC;
+      if (c < S.n) emit(S, c, held + k * VEC, inv);
+    }
+    for (int c = (lane + 32 * GROUPS) * VEC; c < S.n; c += 32 * VEC) {
+      float y[VEC];
+      conv(S.ch0 + c, y);
+      emit(S, c, y, inv);
+    }
+    for (int x = S.n + lane; x < S.width; x += 32) S.dst[x] = from_f<T>(0.f);  // padding: adds nothing to a score or an output
   }
-  for (int c = n + lane; c < width; c += 32) dst[c] = from_f<T>(0.f);  // padding: adds nothing to a score or an output
 }
 
 }  // namespace sinkattn
@@ -444,7 +569,7 @@ DSB_EXPORT int dsb200_latent_rotary_append(void* proj, long long ld, int q_col0,
 
 // Attention inputs behind a short causal convolution.  proj [T, ld] holds from col0 on the query heads [H d], the key heads [G d] and the value
 // heads [G dv] of every token; bias (fp32, that many entries, or null) is added to every row before the convolution with conv_w (fp32
-// [channels, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence's start).  state [slots, taps - 1, channels]: the last
+// [taps, channels]: y_t = sum_j w[j, :] u_(t - taps + 1 + j), zeros before the sequence's start).  state [slots, taps - 1, channels]: the last
 // rows of the sequence's earlier steps, WITHOUT the bias (update it afterwards with dsb200_conv_state_update).  Query / key heads: RMS norm over
 // d with wq / wk [d] shared by the heads -> q_out [T, q_ld] (head h at h * q_row) / the key plane.  Value heads: v_own (null, or [T, G dv])
 // receives the convolved values; with v_other ([T, G dv]) and mix (one float on the device) the cached value is (1 - mix) v + mix v_other.
@@ -460,16 +585,31 @@ DSB_EXPORT int dsb200_conv_head_norm_append(const void* proj, long long ld, int 
                   wk != nullptr && (v_other == nullptr || mix != nullptr),
               "conv_head_norm_append: heads %d / %d, head sizes %d / %d, taps %d", H, G, d, dv, taps);
   DSB_REQUIRE(q_row >= d && k_row >= d && v_row >= dv, "conv_head_norm_append: row widths %d / %d / %d below the head sizes %d / %d", q_row, k_row, v_row, d, dv);
-  const long long warps = static_cast<long long>(n_tokens) * (H + 2 * G);
+  auto mult4 = [](long long v) { return v % 4 == 0; };
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = mult4(d) && mult4(dv) && mult4(ld) && mult4(col0) && mult4(q_ld) && mult4(q_row) && mult4(k_row) && mult4(v_row) && mult4(k_block_stride) &&
+                   mult4(v_block_stride) && al16(proj) && al16(bias) && al16(conv_w) && al16(wq) && al16(wk) && al16(state) && al16(k_cache) && al16(v_cache) && al16(q_out) && al16(v_other) && al16(v_own);
+  // several slots per warp when a lane's first group of channels covers a head and there are enough tokens to fill the GPU all the same
+  const bool many = (d > dv ? d : dv) <= (vec ? 128 : 32) && static_cast<long long>(n_tokens) * (H + 2 * G) >= 16384;
+  const int sl = many ? 4 : 1;
+  const long long warps = static_cast<long long>(n_tokens) * ((H + 2 * G + sl - 1) / sl);
   const int wpb = 8;
   const int grid = static_cast<int>((warps + wpb - 1) / wpb);
-#define LAUNCH(T)                                                                                                                                     \
-  conv_head_norm_append_kernel<T><<<grid, wpb * 32, 0, stream>>>((const T*)proj, ld, col0, bias, conv_w, wq, wk, (const T*)state, (const int4*)seq_desc, tok_seq, \
-                                                                 tok_pos, block_table, bt_stride, block_size, (T*)k_cache, k_block_stride, (T*)v_cache,         \
-                                                                 v_block_stride, (T*)q_out, q_ld, (const T*)v_other, mix, (T*)v_own, n_tokens, H, G, d, dv,     \
-                                                                 taps, eps, q_row, k_row, v_row)
-  if (dtype == 0) LAUNCH(bf16);
-  else LAUNCH(float);
+#define LAUNCH(T, V, S)                                                                                                                                     \
+  conv_head_norm_append_kernel<T, V, S><<<grid, wpb * 32, 0, stream>>>((const T*)proj, ld, col0, bias, conv_w, wq, wk, (const T*)state, (const int4*)seq_desc, tok_seq, \
+                                                                       tok_pos, block_table, bt_stride, block_size, (T*)k_cache, k_block_stride, (T*)v_cache,         \
+                                                                       v_block_stride, (T*)q_out, q_ld, (const T*)v_other, mix, (T*)v_own, n_tokens, H, G, d, dv,     \
+                                                                       taps, eps, q_row, k_row, v_row)
+#define PICK(T)                                                  \
+  do {                                                           \
+    if (vec && many) LAUNCH(T, 4, 4);                            \
+    else if (vec) LAUNCH(T, 4, 1);                               \
+    else if (many) LAUNCH(T, 1, 4);                              \
+    else LAUNCH(T, 1, 1);                                        \
+  } while (0)
+  if (dtype == 0) PICK(bf16);
+  else PICK(float);
+#undef PICK
 #undef LAUNCH
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;

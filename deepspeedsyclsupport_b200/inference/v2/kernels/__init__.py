@@ -838,7 +838,7 @@ def latent_rotary_append(proj, q_col0, kv_col0, wkv, freq, tok_seq, tok_pos, blo
 def conv_head_norm_append(proj, col0, bias, conv_w, wq, wk, state, seq_desc, tok_seq, tok_pos, block_table, block_size, k_plane, v_plane, q_out,
                           H, G, d, dv, taps, eps, v_other=None, mix=None, v_own=None, row=None):
     """Query heads [H d], key heads [G d] and value heads [G dv] lie side by side in proj from column col0.  Every channel gets its bias
-    (fp32, or None) and a short causal convolution (conv_w fp32 [channels, taps]; rows before this step's come from state
+    (fp32, or None) and a short causal convolution (conv_w fp32 [taps, channels]; rows before this step's come from state
     [slots, taps - 1, channels], rows before the sequence are zeros); query / key heads are RMS-normed with wq / wk [d] (shared by the heads);
     queries -> q_out, keys / values -> their planes.  v_own ([T, G dv]): receives the convolved values; v_other + mix (fp32 [1]): the cached
     value is (1 - mix) v + mix v_other.  `row`: heads are padded with zeros to this width."""
@@ -847,6 +847,7 @@ def conv_head_norm_append(proj, col0, bias, conv_w, wq, wk, state, seq_desc, tok
     for v in (v_other, v_own):
         assert v is None or (v.is_contiguous() and v.dtype == proj.dtype and v.shape == (proj.shape[0], G * dv))
     assert state is None or (state.dtype == proj.dtype and state.is_contiguous())
+    assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape == (taps, (H + G) * d + G * dv)
     native.check(native.lib().dsb200_conv_head_norm_append(native.ptr(proj), proj.stride(0), col0, native.ptr(bias), native.ptr(conv_w), native.ptr(wq),
                                                            native.ptr(wk), native.ptr(state), native.ptr(seq_desc), native.ptr(tok_seq),
                                                            native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0), int(block_size),

@@ -100,13 +100,24 @@ class AttentionInputParameter(ParameterBase):
 
 
 class StackedFp32Parameter(ParameterBase):
-    """Per-channel fp32 tensors of the query, key and value projections (biases [channels]; convolution taps [channels, taps]), stacked."""
+    """Per-channel fp32 tensors of the query, key and value projections (their biases), stacked."""
     q: torch.Tensor
     k: torch.Tensor
     v: torch.Tensor
 
     def finalize(self) -> torch.Tensor:
         return self.inference_model.transform_fp32_param(torch.cat([self.q, self.k, self.v], dim=0))
+
+
+class ConvTapsParameter(ParameterBase):
+    """Convolution taps [channels, taps] of the query, key and value projections -> one fp32 tensor [taps, all channels]: the layout the
+    prepare kernel reads (the lanes of a warp read neighbouring channels of one tap)."""
+    q: torch.Tensor
+    k: torch.Tensor
+    v: torch.Tensor
+
+    def finalize(self) -> torch.Tensor:
+        return self.inference_model.transform_fp32_param(torch.cat([self.q, self.k, self.v], dim=0).t())
 
 
 class _MidulornLayerContainer(LayerContainer):
@@ -176,7 +187,7 @@ class MidulornGatedUnitContainer(_MidulornLayerContainer):
 class MidulornAttentionContainer(_MidulornLayerContainer):
     in_w: AttentionInputParameter
     in_bias: StackedFp32Parameter
-    conv_w: StackedFp32Parameter
+    conv_w: ConvTapsParameter
     norm_q: Fp32Parameter
     norm_k: Fp32Parameter
     vmix: Optional[Fp32Parameter]

@@ -92,7 +92,7 @@ class DSConvSinkAttention(DSSelfAttentionBase):
                 v_cache: Optional[torch.Tensor], batch, state_manager, prefix: str, out: torch.Tensor, v_source: Optional[torch.Tensor] = None,
                 mix: Optional[torch.Tensor] = None):
         """proj [T, N]: the fused projection with (queries | keys | values) from column col0 (without their biases: `bias`, fp32, is added
-        here).  k_cache / v_cache: the layer's cache tensor(s) as `cache_shapes` lists them (v_cache None for the two-plane tensor).  out:
+        here); conv_w fp32 [taps, conv_channels].  k_cache / v_cache: the layer's cache tensor(s) as `cache_shapes` lists them (v_cache None for the two-plane tensor).  out:
         [T, out_width] view.  value_mix "mix": v_source = the source layer's values of these tokens, mix = the weight (fp32 [1]).  Returns
         (out, this layer's convolved values when value_mix is "source", else None)."""
         c = self._config

@@ -389,7 +389,7 @@ def _conv_caches(mod, blocks, block, dt):
 def _conv_args(P, dt):
     f = lambda t: t.float().reshape(-1 if t.dim() == 0 else t.shape).cuda()  # noqa: E731
     return dict(w_in=torch.cat([P["mix.q"], P["mix.k"], P["mix.v"]]).to(dt).cuda(), bias=f(torch.cat([P["mix.q.b"], P["mix.k.b"], P["mix.v.b"]])),
-                conv=f(torch.cat([P["mix.q.conv"], P["mix.k.conv"], P["mix.v.conv"]])), nq=f(P["mix.q.norm"]), nk=f(P["mix.k.norm"]), r1=f(P["mix.r1"]),
+                conv=f(torch.cat([P["mix.q.conv"], P["mix.k.conv"], P["mix.v.conv"]]).t().contiguous()), nq=f(P["mix.q.norm"]), nk=f(P["mix.k.norm"]), r1=f(P["mix.r1"]),
                 r2=f(P["mix.r2"]), sink=f(P["mix.sink"]), mix=f(P["mix.vmix"]))
 
 
