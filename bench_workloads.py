@@ -999,7 +999,7 @@ def _midulorn_state(torch, dev, W, L, H, d, hkv, E, top, ff, V):
     kinds = [lat, rec, att, rec]
     layers = [dict(kinds[i % 4], mlp=dense if i == L - 1 else moe) for i in range(L)]
     cfg = {"architecture": "Midulorn", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": W ** 0.5}, "postln_alpha": 2.0,
-           "logit_scale": 0.5, "layers": layers}
+           "logit_scale": 0.25, "layers": layers}
 
     def r(*shape, std=0.02, mean=0.0):
         return torch.empty(*shape, device=dev, dtype=torch.bfloat16).normal_(mean, std)

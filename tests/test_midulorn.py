@@ -177,9 +177,9 @@ def test_norm_behind_the_sum(dim, dt):
     x[4] *= 50
     y, y32, bias, w = torch.randn(9, dim, generator=g).to(dt), torch.randn(9, dim, generator=g), torch.randn(dim, generator=g), 1 + 0.3 * torch.randn(dim, generator=g)
     for use_y, use_32, use_b in ((1, 0, 0), (0, 1, 0), (1, 1, 1), (0, 0, 0)):
-        want = O.join(x.double(), (y.double() if use_y else 0) + (y32.double() if use_32 else 0) + (bias.double() if use_b else 0), w, 2.5, 1e-5)
+        want = O.join(x.double(), (y.double() if use_y else 0) + (y32.double() if use_32 else 0) + (bias.double() if use_b else 0), w, 1.75, 1e-5)
         xs = x.cuda().clone()
-        h = K.post_sum_norm(xs, y.cuda() if use_y else None, w.cuda(), alpha=2.5, eps=1e-5, y32=y32.cuda() if use_32 else None, bias=bias.cuda() if use_b else None,
+        h = K.post_sum_norm(xs, y.cuda() if use_y else None, w.cuda(), alpha=1.75, eps=1e-5, y32=y32.cuda() if use_32 else None, bias=bias.cuda() if use_b else None,
                             out_dtype=dt)
         assert torch.allclose(xs.cpu().double(), want, rtol=1e-5, atol=1e-5)
         assert h.dtype == dt and torch.allclose(h.cpu().double(), want, rtol=1e-5 if dt == torch.float32 else 1e-2, atol=1e-5 if dt == torch.float32 else 1e-2)
@@ -238,7 +238,7 @@ def _run_unit(mod, P, h, cuts, dt, state, slot, pieces=None):
 
 @gpu
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("width", [5, 130, 320])
+@pytest.mark.parametrize("width", [5, 130, 328])
 @pytest.mark.parametrize("sizes,pieces", [([90], None), ([90], False), ([90], True), ([1] * 60, None), ([2, 5, 1, 33, 2, 9], True), ([2, 5, 1, 70, 2, 9], None)])
 def test_minimal_gated_recurrence(width, sizes, pieces, dt):
     """Whole, token by token and in portions down to two tokens, as one walk and cut into pieces, in a slot that held garbage."""
@@ -333,7 +333,7 @@ LATENT_CASES = [
     O.latent_layer(3, 6, 4, 5, 10, scale=0.4, base=300.0)["mixer"],              # odd sizes
     O.latent_layer(2, 8, 8, 8, 24, scale=0.3, rot_dims=4, base=50.0)["mixer"],     # only some of the rotated part's entries are rotated
     O.latent_layer(4, 16, 16, 24, 40, scale=0.25)["mixer"],                       # bf16: row padded to 64, on the tensor cores
-    O.latent_layer(5, 32, 32, 16, 96, scale=0.15, base=1e6)["mixer"],             # bf16: a full row of 128, heads padded to 8
+    O.latent_layer(5, 32, 32, 16, 96, scale=0.15, base=5e5)["mixer"],             # bf16: a full row of 128, heads padded to 8
     O.latent_layer(2, 24, 16, 32, 160, scale=0.2)["mixer"],                       # too wide for the tensor-core kernels: CUDA cores in bf16 too
 ]
 
@@ -551,9 +551,9 @@ CONFIGS = {
         O.latent_layer(4, 16, 16, 32, 40, scale=0.25, mlp=O.dense(256)),
         O.mingru_layer(384, mlp=O.moe(8, 2, 32)),
         O.attention_layer(2, 1, 128, 128, conv=2, part=48, scale=0.12, v_mix=True, mlp=O.dense(128)),
-        O.latent_layer(8, 32, 32, 32, 96, scale=0.15, base=1e6),
+        O.latent_layer(8, 32, 32, 32, 96, scale=0.15, base=5e5),
         O.attention_layer(4, 1, 72, 128, conv=3, part=32, scale=0.15, v_mix=True, mlp=O.dense(64)),
-    ], vocab=96, width=256, eps=1e-6, alpha=2.0, embedding_scale=3.0, logit_scale=0.5),
+    ], vocab=96, width=256, eps=1e-6, alpha=2.0, embedding_scale=3.0, logit_scale=0.4),
     # no attention layer at all: nothing is cached per token, everything lives in the state slots
     "recurrent": O.make_config([O.mingru_layer(24, mlp=O.dense(16)), O.mingru_layer(9, mlp=O.moe(2, 1, 8))], vocab=40, width=24, alpha=1.0, logit_scale=1.0),
     # no recurrent layer and one tap everywhere: no state slots
