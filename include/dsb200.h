@@ -627,7 +627,7 @@ int dsb200_latent_rotary_append(void* proj, long long ld, int q_col0, int kv_col
                                 int rot_dims, float eps, int dtype, dsb200_stream_t stream);
 /* Attention inputs behind a short causal convolution.  proj [T, ld] holds from col0 on the query heads [H d], the key heads [G d] and the value
  * heads [G dv] of every token; bias (fp32, that many entries, or null) is added to every row before the convolution with conv_w (fp32
- * [channels, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence's start).  state [slots, taps - 1, channels]: the last
+ * [taps, channels]: y_t = sum_j w[j, :] u_(t - taps + 1 + j), zeros before the sequence's start).  state [slots, taps - 1, channels]: the last
  * rows of the sequence's earlier steps, WITHOUT the bias (update it afterwards with dsb200_conv_state_update).  Query / key heads: RMS norm over
  * d with wq / wk [d] shared by the heads -> q_out [T, q_ld] (head h at h * q_row) / the key plane.  Value heads: v_own (null, or [T, G dv])
  * receives the convolved values; with v_other ([T, G dv]) and mix (one float on the device) the cached value is (1 - mix) v + mix v_other.
